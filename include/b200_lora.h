@@ -1,0 +1,149 @@
+/*
+ * b200_lora.h - C ABI of the B200 (sm_100a) batched multi-LoRA linear library.
+ *
+ * Every entry point takes plain pointers and sizes; no C++ or torch types cross
+ * this boundary. Pointers documented "device" are CUDA device addresses owned by
+ * the caller, pointers documented "host" are ordinary host arrays read during the
+ * call. `stream` is a `cudaStream_t` passed as `void*` (NULL = legacy default
+ * stream). All launches are asynchronous on that stream and allocate nothing.
+ *
+ * Return value: 0 on success, a negative B200_LORA_E* code otherwise, in which
+ * case nothing was launched and `lora_b200_last_error()` returns a message for the
+ * calling thread.
+ *
+ * Reference interfaces are cited by their path inside the a710128/nanovllm-voxcpm
+ * project (e.g. nanovllm_voxcpm/lora.py:43-54).
+ *
+ * Slab layout (nanovllm_voxcpm/layers/lora.py:289-298,507-511,703-705,828-829):
+ *   lora_A slice  [S, r_max, in ]  row-major, contiguous
+ *   lora_B slice  [S, out_s, r_max] row-major, contiguous
+ * where S = number of adapter slots and r_max the slab rank; rows/columns beyond
+ * a slot's effective rank hold zeros.
+ */
+#ifndef B200_LORA_H_
+#define B200_LORA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_LORA_ABI_VERSION 1
+
+/* element types of x / y / slabs */
+#define B200_LORA_BF16 0
+#define B200_LORA_F16 1
+#define B200_LORA_F32 2
+
+/* kernel selection for lora_b200_add (`impl`) */
+#define B200_LORA_IMPL_AUTO 0    /* choose by shape */
+#define B200_LORA_IMPL_GENERIC 1 /* one CTA per token, any dtype / shape / stride */
+#define B200_LORA_IMPL_BGMV 2    /* fused decode kernel: cluster per slot bucket, bulk-copy ring + mma */
+#define B200_LORA_IMPL_SGMV 3    /* prefill kernels: tcgen05 shrink + tcgen05 expand, scratch from `workspace` */
+
+/* error codes */
+#define B200_LORA_OK 0
+#define B200_LORA_EINVAL (-1)      /* bad argument (shape, alignment, null pointer) */
+#define B200_LORA_EUNSUPPORTED (-2) /* requested impl cannot run this shape / dtype */
+#define B200_LORA_ECUDA (-3)       /* CUDA runtime / driver error at launch */
+#define B200_LORA_EWORKSPACE (-4)  /* workspace too small */
+
+#define B200_LORA_MAX_SLICES 4
+
+/* ABI version of the loaded library (== B200_LORA_ABI_VERSION it was built with).
+ * No counterpart in the reference; lets a binding refuse a stale build. */
+int lora_b200_version(void);
+
+/* Message for the last non-zero return on this thread (never NULL). */
+const char* lora_b200_last_error(void);
+
+/*
+ * y[t, col_offsets[s] : col_offsets[s]+out_sizes[s]] +=
+ *        scaling * scale_per_slot[slot_t] * (x[t] . A_s[slot_t]^T) . B_s[slot_t]^T
+ * for every token t with slot_t = token_to_slot[t] >= 0, in place. Rows with
+ * slot_t < 0 are never read or written (their bits are preserved).
+ *
+ * Replaces `LoRABackend.add_lora` / `_VendoredTritonPunicaBackend.add_lora`
+ * (nanovllm_voxcpm/lora.py:43-54, :241-381), i.e. `lora_shrink` + `lora_expand`
+ * (nanovllm_voxcpm/lora_ops/triton_ops/lora_shrink_op.py:257-341,
+ *  lora_expand_op.py:94-170) with add_inputs=True, all slices in one call.
+ *
+ *  y, x            device; [T, *] matrices with row strides y_ld / x_ld (elements),
+ *                  unit column stride.
+ *  a_slabs,b_slabs host arrays of n_slices device pointers (layout above).
+ *  out_sizes       host[n_slices]; width of each slice (0 = slice skipped).
+ *  col_offsets     host[n_slices]; first y column of each slice.
+ *  rank_per_slot   device int32[S] or NULL: effective rank per slot (an optimisation
+ *                  only: slab padding is zero, results are identical).
+ *  scale_per_slot  device float[S] or NULL (= 1).
+ *  token_to_slot   device int32[T]; slot id or -1        (LoRAMetadata.token_to_slot,
+ *                  nanovllm_voxcpm/lora.py:18-37).
+ *  sorted_idx      device int32[<=T] or NULL: token rows grouped by bucket
+ *  slot_ids        device int32[n_buckets] or NULL: slot id per bucket (-1 = unused)
+ *  counts          device int32[n_buckets] or NULL: tokens per bucket
+ *  offsets         device int32[n_buckets+1] or NULL: bucket start in sorted_idx
+ *                  (the reference's token_indices_sorted_by_slot / active_slot_ids /
+ *                  num_tokens_per_slot / slot_start_offsets; any of its three
+ *                  conventions: eager plan, graph buffers with a leading -1 bucket,
+ *                  vLLM-style with a counted -1 bucket). With the bucket arrays NULL
+ *                  only the generic kernel can run.
+ *  workspace       device scratch for B200_LORA_IMPL_SGMV (see
+ *                  lora_b200_workspace_bytes), otherwise may be NULL.
+ */
+int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
+                  int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
+                  const int32_t* out_sizes, const int32_t* col_offsets, int32_t S, int32_t r_max,
+                  const int32_t* rank_per_slot, const float* scale_per_slot,
+                  const int32_t* token_to_slot, const int32_t* sorted_idx, const int32_t* slot_ids,
+                  const int32_t* counts, const int32_t* offsets, int32_t n_buckets, float scaling,
+                  int32_t dtype, int32_t impl, void* workspace, size_t workspace_bytes,
+                  void* stream);
+
+/*
+ * out[s, t, 0:r_max] = scaling * x[t] . A_s[slot_t]^T for slot_t >= 0, and 0 for
+ * rows with slot_t < 0 (the reference zero-fills the buffer first,
+ * lora_shrink_op.py:229,295).
+ *
+ * Replaces `lora_shrink` (nanovllm_voxcpm/lora_ops/triton_ops/lora_shrink_op.py:257-341).
+ *  out        device; [n_slices, T, r_max] contiguous; element type out_dtype
+ *             (B200_LORA_F32 is accepted for any input dtype: used by the
+ *             row-parallel [T, r] all-reduce).
+ */
+int lora_b200_shrink(void* out, int32_t out_dtype, const void* x, int64_t x_ld, int32_t T,
+                     int32_t in_dim, int32_t n_slices, const void* const* a_slabs, int32_t S,
+                     int32_t r_max, const int32_t* token_to_slot, float scaling, int32_t dtype,
+                     void* stream);
+
+/*
+ * y[t, offset_start + sum(out_sizes[:s]) + c] (+)= tmp[s, t, :] . B_s[slot_t][c, :]
+ * for slot_t >= 0; `add_inputs` = 0 overwrites instead of accumulating.
+ *
+ * Replaces `lora_expand` (nanovllm_voxcpm/lora_ops/triton_ops/lora_expand_op.py:94-170).
+ *  tmp        device; [n_slices, T, r_max] contiguous, element type tmp_dtype.
+ */
+int lora_b200_expand(void* y, int64_t y_ld, const void* tmp, int32_t tmp_dtype, int32_t T,
+                     int32_t n_slices, const void* const* b_slabs, const int32_t* out_sizes,
+                     const int32_t* col_offsets, int32_t S, int32_t r_max,
+                     const int32_t* token_to_slot, int32_t add_inputs, int32_t dtype,
+                     void* stream);
+
+/* Tuning knobs of the fused decode kernel (process-wide, read at launch time). */
+#define B200_LORA_OPT_CLUSTER 1 /* CTAs per slot bucket: 1, 2, 4, 8; 0 = choose from n_buckets */
+#define B200_LORA_OPT_PDL 2     /* 1 = launch with programmatic stream serialization (default), 0 = off */
+
+/* Sets a tuning knob; returns 0, or B200_LORA_EINVAL for an unknown key / value.
+ * No counterpart in the reference (its tile configs are static tables,
+ * nanovllm_voxcpm/lora_ops/triton_ops/utils.py:119-150). */
+int lora_b200_set_option(int32_t key, int32_t value);
+
+/* Reads (and, if `reset` != 0, clears) the status word of the current device into
+ * *status: 0 = no kernel ever gave up a bounded wait. Synchronises the device; meant
+ * for tests and health checks, not for the hot path. No counterpart in the reference. */
+int lora_b200_device_status(int32_t* status, int32_t reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_LORA_H_ */

@@ -1,0 +1,145 @@
+"""ctypes binding of the C-ABI library (``lib/libb200lora.so``).
+
+The library is the only compute path of this package: there is no Python or
+CPU fallback. Importing this module without the built library raises; calling a
+launch function without a CUDA device raises.  The C declarations live in
+``include/b200_lora.h``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_float, c_int32, c_int64, c_size_t, c_void_p
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libb200lora.so")
+
+ABI_VERSION = 1
+
+DT_BF16, DT_F16, DT_F32 = 0, 1, 2
+IMPL_AUTO, IMPL_GENERIC, IMPL_BGMV, IMPL_SGMV = 0, 1, 2, 3
+MAX_SLICES = 4
+
+E_INVAL, E_UNSUPPORTED, E_CUDA, E_WORKSPACE = -1, -2, -3, -4
+
+_DTYPES = {torch.bfloat16: DT_BF16, torch.float16: DT_F16, torch.float32: DT_F32}
+
+#: every symbol declared in include/b200_lora.h, with (restype, argtypes)
+_SIGNATURES = {
+    "lora_b200_version": (c_int32, []),
+    "lora_b200_last_error": (c_char_p, []),
+    "lora_b200_add": (
+        c_int32,
+        [c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32, POINTER(c_void_p), POINTER(c_void_p),
+         POINTER(c_int32), POINTER(c_int32), c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_int32, c_float, c_int32, c_int32, c_void_p, c_size_t, c_void_p],
+    ),
+    "lora_b200_shrink": (
+        c_int32,
+        [c_void_p, c_int32, c_void_p, c_int64, c_int32, c_int32, c_int32, POINTER(c_void_p), c_int32, c_int32,
+         c_void_p, c_float, c_int32, c_void_p],
+    ),
+    "lora_b200_expand": (
+        c_int32,
+        [c_void_p, c_int64, c_void_p, c_int32, c_int32, c_int32, POINTER(c_void_p), POINTER(c_int32),
+         POINTER(c_int32), c_int32, c_int32, c_void_p, c_int32, c_int32, c_void_p],
+    ),
+    "lora_b200_set_option": (c_int32, [c_int32, c_int32]),
+    "lora_b200_device_status": (c_int32, [POINTER(c_int32), c_int32]),
+}
+
+OPT_CLUSTER, OPT_PDL = 1, 2
+
+
+class NativeLibraryError(RuntimeError):
+    pass
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise NativeLibraryError(
+            f"{LIB_PATH} is missing: build it with `python -m nanovllm_voxcpm_b200.build` "
+            "(nvcc, sm_100a). This package has no fallback path."
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the build is stale
+        fn.restype = restype
+        fn.argtypes = argtypes
+    got = lib.lora_b200_version()
+    if got != ABI_VERSION:
+        raise NativeLibraryError(f"{LIB_PATH} has ABI version {got}, this package needs {ABI_VERSION}: rebuild it")
+    return lib
+
+
+_LIB: ctypes.CDLL | None = None
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        _LIB = _load()
+    return _LIB
+
+
+def exported_symbols() -> list[str]:
+    return list(_SIGNATURES)
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"unsupported LoRA dtype {dtype}; expected bfloat16, float16 or float32") from None
+
+
+def check(rc: int) -> None:
+    """Map a C status to the exceptions the reference raises before launch."""
+    if rc == 0:
+        return
+    msg = lib().lora_b200_last_error().decode("utf-8", "replace")
+    if rc == E_INVAL:
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+def require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "nanovllm_voxcpm_b200 runs on CUDA tensors only (sm_100a kernels, no CPU fallback); "
+                f"got a tensor on {t.device}"
+            )
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def ptr_array(tensors) -> ctypes.Array:
+    arr = (c_void_p * len(tensors))()
+    for i, t in enumerate(tensors):
+        arr[i] = t.data_ptr() if t is not None else None
+    return arr
+
+
+def int_array(values) -> ctypes.Array:
+    return (c_int32 * len(values))(*[int(v) for v in values])
+
+
+def current_stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def set_option(key: int, value: int) -> None:
+    check(lib().lora_b200_set_option(key, value))
+
+
+def device_status(reset: bool = False) -> int:
+    """Status word of the current CUDA device (0 = healthy); synchronises."""
+    out = c_int32(0)
+    check(lib().lora_b200_device_status(ctypes.byref(out), 1 if reset else 0))
+    return out.value

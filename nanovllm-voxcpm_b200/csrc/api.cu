@@ -1,0 +1,227 @@
+// C ABI of the B200 multi-LoRA library: argument checks + kernel dispatch.
+// Declarations and the reference interface each entry point replaces: include/b200_lora.h
+#include "common.cuh"
+#include "generic.cuh"
+#include "bgmv_fused.cuh"
+
+using namespace b200lora;
+
+namespace {
+
+int fill_slices(SliceTable& st, int n_slices, const void* const* a_slabs,
+                const void* const* b_slabs, const int32_t* out_sizes,
+                const int32_t* col_offsets, bool need_a, bool need_b) {
+  if (n_slices < 1 || n_slices > B200_LORA_MAX_SLICES)
+    return fail(B200_LORA_EINVAL, "n_slices=%d outside [1,%d]", n_slices, B200_LORA_MAX_SLICES);
+  st.n = n_slices;
+  for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) {
+    st.a[s] = st.b[s] = nullptr;
+    st.out[s] = st.col[s] = 0;
+  }
+  for (int s = 0; s < n_slices; ++s) {
+    st.out[s] = out_sizes ? out_sizes[s] : 1;
+    st.col[s] = col_offsets ? col_offsets[s] : 0;
+    if (st.out[s] < 0 || st.col[s] < 0)
+      return fail(B200_LORA_EINVAL, "slice %d: negative width/offset", s);
+    if (need_a) {
+      st.a[s] = a_slabs ? a_slabs[s] : nullptr;
+      if (st.a[s] == nullptr && st.out[s] > 0) return fail(B200_LORA_EINVAL, "slice %d: null lora_A slab", s);
+    }
+    if (need_b) {
+      st.b[s] = b_slabs ? b_slabs[s] : nullptr;
+      if (st.b[s] == nullptr && st.out[s] > 0) return fail(B200_LORA_EINVAL, "slice %d: null lora_B slab", s);
+    }
+  }
+  return B200_LORA_OK;
+}
+
+bool valid_dtype(int d) { return d == B200_LORA_BF16 || d == B200_LORA_F16 || d == B200_LORA_F32; }
+
+template <typename T>
+int launch_generic_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int T_rows, int in_dim,
+                       const SliceTable& st, int S, int r_max, const int32_t* rank_per_slot,
+                       const float* scale_per_slot, const int32_t* token_to_slot, float scaling,
+                       cudaStream_t stream) {
+  const size_t smem = sizeof(float) * st.n * r_max;
+  generic_add_kernel<T><<<T_rows, kGenericThreads, smem, stream>>>(
+      static_cast<T*>(y), y_ld, static_cast<const T*>(x), x_ld, in_dim, st, S, r_max,
+      rank_per_slot, scale_per_slot, token_to_slot, scaling);
+  return check_launch("generic_add_kernel");
+}
+
+template <typename T, typename TO>
+int launch_generic_shrink(void* out, const void* x, int64_t x_ld, int T_rows, int in_dim,
+                          const SliceTable& st, int S, int r_max, const int32_t* token_to_slot,
+                          float scaling, cudaStream_t stream) {
+  generic_shrink_kernel<T, TO><<<T_rows, kGenericThreads, 0, stream>>>(
+      static_cast<TO*>(out), static_cast<const T*>(x), x_ld, T_rows, in_dim, st, S, r_max,
+      token_to_slot, scaling);
+  return check_launch("generic_shrink_kernel");
+}
+
+template <typename T, typename TI>
+int launch_generic_expand(void* y, int64_t y_ld, const void* tmp, int T_rows, const SliceTable& st,
+                          int S, int r_max, const int32_t* token_to_slot, int add_inputs,
+                          cudaStream_t stream) {
+  const size_t smem = sizeof(float) * st.n * r_max;
+  generic_expand_kernel<T, TI><<<T_rows, kGenericThreads, smem, stream>>>(
+      static_cast<T*>(y), y_ld, static_cast<const TI*>(tmp), T_rows, st, S, r_max, token_to_slot,
+      add_inputs);
+  return check_launch("generic_expand_kernel");
+}
+
+}  // namespace
+
+extern "C" {
+
+int lora_b200_version(void) { return B200_LORA_ABI_VERSION; }
+
+const char* lora_b200_last_error(void) { return error_buffer(); }
+
+int lora_b200_set_option(int32_t key, int32_t value) {
+  if (key == B200_LORA_OPT_CLUSTER) {
+    if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8)
+      return fail(B200_LORA_EINVAL, "cluster size %d not in {0,1,2,4,8}", value);
+    bgmv_options().cluster = value;
+    return B200_LORA_OK;
+  }
+  if (key == B200_LORA_OPT_PDL) {
+    bgmv_options().pdl = value != 0;
+    return B200_LORA_OK;
+  }
+  return fail(B200_LORA_EINVAL, "unknown option %d", key);
+}
+
+int lora_b200_device_status(int32_t* status, int32_t reset) {
+  if (status == nullptr) return fail(B200_LORA_EINVAL, "null status pointer");
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_b200_status, sizeof(int));
+  if (e != cudaSuccess) return fail(B200_LORA_ECUDA, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
+  *status = v;
+  if (reset) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_b200_status, &zero, sizeof(int));
+    if (e != cudaSuccess) return fail(B200_LORA_ECUDA, "cudaMemcpyToSymbol: %s", cudaGetErrorString(e));
+  }
+  return B200_LORA_OK;
+}
+
+int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
+                  int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
+                  const int32_t* out_sizes, const int32_t* col_offsets, int32_t S, int32_t r_max,
+                  const int32_t* rank_per_slot, const float* scale_per_slot,
+                  const int32_t* token_to_slot, const int32_t* sorted_idx, const int32_t* slot_ids,
+                  const int32_t* counts, const int32_t* offsets, int32_t n_buckets, float scaling,
+                  int32_t dtype, int32_t impl, void* workspace, size_t workspace_bytes,
+                  void* stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  if (!valid_dtype(dtype)) return fail(B200_LORA_EINVAL, "unknown dtype %d", dtype);
+  if (T < 0 || in_dim < 1 || S < 1 || r_max < 1)
+    return fail(B200_LORA_EINVAL, "bad sizes T=%d in=%d S=%d r_max=%d", T, in_dim, S, r_max);
+  if (T == 0) return B200_LORA_OK;
+  if (y == nullptr || x == nullptr || token_to_slot == nullptr)
+    return fail(B200_LORA_EINVAL, "null y / x / token_to_slot");
+  if (out_sizes == nullptr || col_offsets == nullptr)
+    return fail(B200_LORA_EINVAL, "null out_sizes / col_offsets");
+  SliceTable st;
+  if (int rc = fill_slices(st, n_slices, a_slabs, b_slabs, out_sizes, col_offsets, true, true)) return rc;
+  int64_t width = 0;
+  bool any = false;
+  for (int s = 0; s < st.n; ++s) {
+    width = width > (int64_t)st.col[s] + st.out[s] ? width : (int64_t)st.col[s] + st.out[s];
+    any = any || st.out[s] > 0;
+  }
+  if (!any) return B200_LORA_OK;
+  if (y_ld < width || x_ld < in_dim)
+    return fail(B200_LORA_EINVAL, "row stride smaller than row: y_ld=%lld (need %lld) x_ld=%lld (need %d)",
+                (long long)y_ld, (long long)width, (long long)x_ld, in_dim);
+  cudaStream_t st_ = static_cast<cudaStream_t>(stream);
+  const bool have_buckets = sorted_idx && slot_ids && counts && offsets && n_buckets > 0;
+
+  BgmvProblem bp;
+  bp.y = y; bp.y_ld = y_ld; bp.x = x; bp.x_ld = x_ld; bp.T = T; bp.in_dim = in_dim; bp.st = st;
+  bp.S = S; bp.r_max = r_max; bp.rank_per_slot = rank_per_slot; bp.scale_per_slot = scale_per_slot;
+  bp.sorted_idx = sorted_idx; bp.slot_ids = slot_ids; bp.counts = counts; bp.offsets = offsets;
+  bp.n_buckets = n_buckets; bp.scaling = scaling;
+
+  if (impl == B200_LORA_IMPL_AUTO) {
+    impl = (dtype == B200_LORA_BF16 && have_buckets && bgmv_supported(bp, nullptr)) ? B200_LORA_IMPL_BGMV
+                                                                                    : B200_LORA_IMPL_GENERIC;
+  }
+  switch (impl) {
+    case B200_LORA_IMPL_GENERIC:
+      if (r_max > 2048) return fail(B200_LORA_EUNSUPPORTED, "generic kernel: r_max=%d > 2048", r_max);
+      if (dtype == B200_LORA_BF16)
+        return launch_generic_add<__nv_bfloat16>(y, y_ld, x, x_ld, T, in_dim, st, S, r_max, rank_per_slot,
+                                                 scale_per_slot, token_to_slot, scaling, st_);
+      if (dtype == B200_LORA_F16)
+        return launch_generic_add<__half>(y, y_ld, x, x_ld, T, in_dim, st, S, r_max, rank_per_slot,
+                                          scale_per_slot, token_to_slot, scaling, st_);
+      return launch_generic_add<float>(y, y_ld, x, x_ld, T, in_dim, st, S, r_max, rank_per_slot,
+                                       scale_per_slot, token_to_slot, scaling, st_);
+    case B200_LORA_IMPL_BGMV: {
+      if (dtype != B200_LORA_BF16) return fail(B200_LORA_EUNSUPPORTED, "fused decode kernel is bf16 only");
+      if (!have_buckets) return fail(B200_LORA_EINVAL, "fused decode kernel needs the bucket arrays");
+      const char* why = nullptr;
+      if (!bgmv_supported(bp, &why)) return fail(B200_LORA_EUNSUPPORTED, "fused decode kernel: %s", why);
+      return bgmv_launch(bp, st_);
+    }
+    default:
+      return fail(B200_LORA_EUNSUPPORTED, "impl %d is not available", impl);
+  }
+}
+
+int lora_b200_shrink(void* out, int32_t out_dtype, const void* x, int64_t x_ld, int32_t T,
+                     int32_t in_dim, int32_t n_slices, const void* const* a_slabs, int32_t S,
+                     int32_t r_max, const int32_t* token_to_slot, float scaling, int32_t dtype,
+                     void* stream) {
+  if (!valid_dtype(dtype) || !valid_dtype(out_dtype)) return fail(B200_LORA_EINVAL, "unknown dtype");
+  if (out_dtype != dtype && out_dtype != B200_LORA_F32)
+    return fail(B200_LORA_EUNSUPPORTED, "shrink output must have the input dtype or be f32");
+  if (T < 0 || in_dim < 1 || S < 1 || r_max < 1) return fail(B200_LORA_EINVAL, "bad sizes");
+  if (T == 0) return B200_LORA_OK;
+  if (!out || !x || !token_to_slot) return fail(B200_LORA_EINVAL, "null out / x / token_to_slot");
+  if (x_ld < in_dim) return fail(B200_LORA_EINVAL, "x_ld < in_dim");
+  SliceTable st;
+  if (int rc = fill_slices(st, n_slices, a_slabs, nullptr, nullptr, nullptr, true, false)) return rc;
+  cudaStream_t st_ = static_cast<cudaStream_t>(stream);
+#define B200_SHRINK(TT)                                                                              \
+  (out_dtype == B200_LORA_F32 && dtype != B200_LORA_F32)                                             \
+      ? launch_generic_shrink<TT, float>(out, x, x_ld, T, in_dim, st, S, r_max, token_to_slot, scaling, st_) \
+      : launch_generic_shrink<TT, TT>(out, x, x_ld, T, in_dim, st, S, r_max, token_to_slot, scaling, st_)
+  if (dtype == B200_LORA_BF16) return B200_SHRINK(__nv_bfloat16);
+  if (dtype == B200_LORA_F16) return B200_SHRINK(__half);
+  return launch_generic_shrink<float, float>(out, x, x_ld, T, in_dim, st, S, r_max, token_to_slot, scaling, st_);
+#undef B200_SHRINK
+}
+
+int lora_b200_expand(void* y, int64_t y_ld, const void* tmp, int32_t tmp_dtype, int32_t T,
+                     int32_t n_slices, const void* const* b_slabs, const int32_t* out_sizes,
+                     const int32_t* col_offsets, int32_t S, int32_t r_max,
+                     const int32_t* token_to_slot, int32_t add_inputs, int32_t dtype,
+                     void* stream) {
+  if (!valid_dtype(dtype) || !valid_dtype(tmp_dtype)) return fail(B200_LORA_EINVAL, "unknown dtype");
+  if (tmp_dtype != dtype && tmp_dtype != B200_LORA_F32)
+    return fail(B200_LORA_EUNSUPPORTED, "expand input must have the weight dtype or be f32");
+  if (T < 0 || S < 1 || r_max < 1) return fail(B200_LORA_EINVAL, "bad sizes");
+  if (T == 0) return B200_LORA_OK;
+  if (!y || !tmp || !token_to_slot || !out_sizes || !col_offsets)
+    return fail(B200_LORA_EINVAL, "null pointer argument");
+  if (r_max > 2048) return fail(B200_LORA_EUNSUPPORTED, "r_max=%d > 2048", r_max);
+  SliceTable st;
+  if (int rc = fill_slices(st, n_slices, nullptr, b_slabs, out_sizes, col_offsets, false, true)) return rc;
+  for (int s = 0; s < st.n; ++s)
+    if (y_ld < (int64_t)st.col[s] + st.out[s]) return fail(B200_LORA_EINVAL, "y_ld smaller than slice end");
+  cudaStream_t st_ = static_cast<cudaStream_t>(stream);
+#define B200_EXPAND(TT)                                                                               \
+  (tmp_dtype == B200_LORA_F32 && dtype != B200_LORA_F32)                                              \
+      ? launch_generic_expand<TT, float>(y, y_ld, tmp, T, st, S, r_max, token_to_slot, add_inputs, st_) \
+      : launch_generic_expand<TT, TT>(y, y_ld, tmp, T, st, S, r_max, token_to_slot, add_inputs, st_)
+  if (dtype == B200_LORA_BF16) return B200_EXPAND(__nv_bfloat16);
+  if (dtype == B200_LORA_F16) return B200_EXPAND(__half);
+  return launch_generic_expand<float, float>(y, y_ld, tmp, T, st, S, r_max, token_to_slot, add_inputs, st_);
+#undef B200_EXPAND
+}
+
+}  // extern "C"
