@@ -1,0 +1,400 @@
+"""Benchmark of the multi-LoRA linear hot path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Workload (N=1 headline): the decode BGMV configuration - 256 sequences x 1 token through
+the LoRA ops of a MiniCPM-style layer (hidden 1024, qkv out 1280, intermediate 4096; qkv /
+o / gate_up / down, 7 projections), 32 adapters of rank 32 in bf16, slots uniform with 10 %
+of rows without adapter.  One STEP = the four multi-LoRA launches of each of 24 layers
+(96 launches) over 24 distinct slab sets (1.07 GB), so the weights of a launch are never
+in L2 from the previous step (126 MB L2): inputs larger than L2 is the cache-defeat method.
+
+  value      GB/s of ALGORITHMIC bytes (each active slot's A and B once, x rows, y read +
+             write for rows with an adapter) with everything resident in HBM; the step is
+             replayed as one CUDA graph and timed with CUDA events.
+  e2e        the same metric through the public backend call (`B200LoRABackend.add_lora`)
+             with host buffers: every call copies x and y from pinned host memory and reads
+             y back, all inside the timed region.
+  roofline   HBM roofline of the dominant kernel (bgmv_fused_kernel): algorithmic bytes per
+             launch / average launch duration, against the measured copy bandwidth.
+  cpu_baseline / --impl reference
+             the reference's pure-PyTorch per-slot LoRA formula (the CPU oracle) on the
+             host cores, on a bounded sample of the same workload (one layer per step).
+
+With N > 1 (torchrun) every rank runs the same workload on its own GPU (request-level
+replicas, no data-path collective): weak scaling, value = sum over ranks / max time.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "multi-LoRA linear GB/s (decode BGMV, algorithmic bytes)"
+N_LAYERS = 24
+T_DECODE, N_SLOTS, RANK, P_NONE = 256, 32, 32, 0.1
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=N_LAYERS)
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def config_dict(layers):
+    return {
+        "workload": "decode_bgmv: 256 seq x 1 token, hidden 1024, qkv 1280, inter 4096, 7 projections, "
+                    "32 adapters rank 32 bf16, 10% rows without adapter",
+        "layers_per_step": layers,
+        "launches_per_step": 4 * layers,
+        "cache_defeat": "inputs larger than L2 (distinct slab set per layer, %.2f GB per step)" % (layers * 44.56e6 / 1e9),
+        "metadata": "cuda-graph buffers (max_loras+1 buckets)",
+        "parallelism": "replicas",
+    }
+
+
+# ------------------------------------------------------------------ CPU baseline
+def cpu_layer_inputs(seed=0):
+    from nanovllm_voxcpm_b200 import workloads as W
+
+    projs = [W.decode_projection(name, seed=seed + i, T=T_DECODE, S=N_SLOTS, r=RANK, p_none=P_NONE)
+             for i, name in enumerate(W.DECODE_LAYER)]
+    slots = projs[0].token_to_slot
+    for p in projs:
+        p.token_to_slot = slots
+    return projs
+
+
+def time_cpu_oracle(steps, warmup, budget_s=None):
+    """Reference formula on the host cores; one step = one layer (4 projections)."""
+    from nanovllm_voxcpm_b200 import workloads as W
+    from oracle import lora_oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    projs = cpu_layer_inputs()
+    # fp32 copies so the timed part is the formula, not dtype conversion
+    prepared = [(p.y.float(), p.x.float(), [a.float() for a in p.a_slabs], [b.float() for b in p.b_slabs],
+                 p.token_to_slot, p.col_offsets) for p in projs]
+    nbytes = sum(W.algorithmic_bytes(p) for p in projs)
+
+    def step():
+        for y, x, a, b, slots, cols in prepared:
+            O.add_lora(y, x, a, b, slots, 1.0, cols)
+
+    for _ in range(warmup):
+        step()
+    times = []
+    t_begin = time.perf_counter()
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+        if budget_s is not None and time.perf_counter() - t_begin > budget_s:
+            break
+    med = statistics.median(times)
+    return dict(gbs=nbytes / med / 1e9, ms=med * 1e3, iters=len(times), bytes=nbytes, cores=torch.get_num_threads())
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    r = time_cpu_oracle(args.steps, args.warmup)
+    sample = "one layer (4 multi-LoRA projections, 58 MB algorithmic) per step, fp32, torch CPU, per-slot formula"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["gbs"], "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": r["iters"], "warmup": args.warmup, "ms_per_step": r["ms"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": config_dict(args.layers),
+        "cpu_baseline": {"value": r["gbs"], "unit": "GB/s", "cores": r["cores"], "kind": "port", "sample": sample},
+        "e2e": {"value": r["gbs"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------- GPU arm
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for row in open(self.path):
+                f = [c.strip() for c in row.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return out
+
+
+def build_gpu_workload(device, layers):
+    """Per layer and projection: device-resident x, y, slabs (distinct per layer)."""
+    from nanovllm_voxcpm_b200 import workloads as W
+
+    gen = torch.Generator(device=device).manual_seed(1234)
+    cpu_gen = torch.Generator().manual_seed(0)
+    slots = W.uniform_slots(cpu_gen, T_DECODE, N_SLOTS, P_NONE)
+    work = []
+    for _ in range(layers):
+        layer = []
+        for name, (in_dim, outs) in W.DECODE_LAYER.items():
+            rn = lambda *s, std=0.02: (torch.randn(*s, generator=gen, device=device) * std).to(torch.bfloat16)  # noqa: E731
+            a = [rn(N_SLOTS, RANK, in_dim) for _ in outs]
+            b = [rn(N_SLOTS, o, RANK) for o in outs]
+            x = rn(T_DECODE, in_dim, std=1.0)
+            y = rn(T_DECODE, sum(outs), std=1.0)
+            cols = [sum(outs[:i]) for i in range(len(outs))]
+            layer.append(dict(name=name, x=x, y=y, a=a, b=b, outs=list(outs), cols=cols))
+        work.append(layer)
+    return slots, work
+
+
+def projection_bytes(slots, in_dim, outs):
+    active = int(torch.unique(slots[slots >= 0]).numel())
+    t_lora = int((slots >= 0).sum())
+    n = len(outs)
+    return 2 * (active * (n * RANK * in_dim + sum(outs) * RANK) + t_lora * in_dim + 2 * t_lora * sum(outs))
+
+
+def run_gpu_arm(args):
+    import torch.distributed as dist
+
+    from nanovllm_voxcpm_b200 import _native as N
+    from nanovllm_voxcpm_b200 import batch_plan as BP
+    from nanovllm_voxcpm_b200 import lora as LORA
+    from nanovllm_voxcpm_b200 import workloads as W
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the product has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    backend = LORA.B200LoRABackend()
+    status = backend.availability()
+    if not status.available:
+        raise RuntimeError(f"B200 LoRA backend unavailable: {status.reason}")
+
+    slots, work = build_gpu_workload(device, args.layers)
+    bufs = BP.GraphLoRABuffers.make(T_DECODE, N_SLOTS, device=device)
+    bufs.load_plan(BP.build_lora_batch_plan_from_token_to_slot({}, slots.tolist()))
+    ctx = bufs.context(T_DECODE)
+    meta = LORA.LoRAMetadata(ctx.token_to_slot, ctx.token_indices_sorted_by_slot, ctx.active_slot_ids,
+                             ctx.num_tokens_per_slot, ctx.slot_start_offsets, False, ctx.num_active_loras)
+    bytes_per_layer = sum(projection_bytes(slots, i, o) for i, o in W.DECODE_LAYER.values())
+    bytes_per_step = bytes_per_layer * args.layers
+    launches_per_step = 4 * args.layers
+
+    def step():
+        for layer in work:
+            for p in layer:
+                LORA.launch_add(p["y"], p["x"], p["a"], p["b"], p["outs"], p["cols"], meta, 1.0, impl=N.IMPL_BGMV)
+
+    stream = torch.cuda.Stream(device)
+    launch_mode = "eager"
+    graph = None
+    with torch.cuda.stream(stream):
+        step()
+        stream.synchronize()
+        if not args.no_graph:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    step()
+                launch_mode = "cuda_graph"
+            except Exception as exc:  # capture not possible: time eager launches instead
+                graph = None
+                launch_mode = f"eager (graph capture failed: {type(exc).__name__})"
+                torch.cuda.synchronize()
+    run_step = graph.replay if graph is not None else step
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    sampler = ClockSampler(local)
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            run_step()
+        barrier()
+        sampler.start()
+        t_wall = time.perf_counter()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(args.steps):
+            run_step()
+        end.record(stream)
+        end.synchronize()
+        # keep the sampler alive long enough to take a few readings under load
+        while time.perf_counter() - t_wall < 0.6:
+            run_step()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+        barrier()
+    elapsed_ms = start.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    value = bytes_per_step * world / (ms_per_step * 1e-3) / 1e9
+
+    # ---- e2e: public backend call with host buffers ---------------------------------
+    e2e = None
+    if not args.no_e2e:
+        host = []
+        for p in work[0]:
+            host.append(dict(x=p["x"].cpu().pin_memory(), y=p["y"].cpu().pin_memory(),
+                             out=torch.empty_like(p["y"], device="cpu").pin_memory()))
+        h2d = sum(h["x"].numel() * 2 + h["y"].numel() * 2 for h in host) * args.layers
+        d2h = sum(h["out"].numel() * 2 for h in host) * args.layers
+        eager_meta = None
+
+        def e2e_step():
+            for layer in work:
+                for p, h in zip(layer, host):
+                    p["x"].copy_(h["x"], non_blocking=True)
+                    p["y"].copy_(h["y"], non_blocking=True)
+                    backend.add_lora(list(p["y"].split(p["outs"], dim=-1)), p["x"], p["a"], p["b"],
+                                     indices=meta.token_to_slot, metadata=meta, scaling=1.0, y_packed=p["y"])
+                    h["out"].copy_(p["y"], non_blocking=True)
+
+        with torch.cuda.stream(stream):
+            for _ in range(min(args.warmup, 3)):
+                e2e_step()
+            barrier()
+            s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n_e2e = max(3, min(args.steps, 10))
+            s2.record(stream)
+            for _ in range(n_e2e):
+                e2e_step()
+            e2.record(stream)
+            e2.synchronize()
+            barrier()
+        e2e_ms = s2.elapsed_time(e2)
+        if world > 1:
+            t = torch.tensor([e2e_ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        del eager_meta
+        e2e = {"value": bytes_per_step * world / (e2e_ms / n_e2e * 1e-3) / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / n_e2e, "steps": n_e2e}
+
+    status_word = N.device_status()
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        per_launch_s = ms_per_step * 1e-3 / launches_per_step
+        achieved = bytes_per_step / launches_per_step / per_launch_s / 1e9
+        traffic = None
+        try:
+            with open(os.path.join(ROOT, "profiles", "roofline_traffic.json")) as f:
+                traffic = json.load(f).get("bgmv_fused_kernel_bytes_per_launch")
+        except Exception:
+            pass
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_dict(args.layers),
+            "launch_mode": launch_mode, "gpu_launches": launches_per_step * args.steps,
+            "tokens_per_s": T_DECODE * args.layers * world / (ms_per_step * 1e-3),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "bgmv_fused_kernel",
+                         "us_per_launch": per_launch_s * 1e6, "algorithmic_bytes_per_launch": bytes_per_step / launches_per_step,
+                         "frac_of_nominal_8TBs": achieved / 8000.0},
+            "clocks": clocks, "device_status": status_word,
+        }
+        if e2e is not None:
+            line["e2e"] = e2e
+        if world == 1 and not args.no_cpu_baseline:
+            r = time_cpu_oracle(steps=40, warmup=3, budget_s=15.0)
+            line["cpu_baseline"] = {
+                "value": r["gbs"], "unit": "GB/s", "cores": r["cores"], "kind": "port",
+                "sample": f"one layer (4 projections, {r['bytes'] / 1e6:.1f} MB algorithmic) x {r['iters']} iterations, "
+                          f"fp32 torch CPU per-slot formula, median {r['ms']:.2f} ms",
+            }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

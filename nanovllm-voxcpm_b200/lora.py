@@ -128,7 +128,7 @@ def launch_add(
     S, r_max, in_dim = a_slabs[0].shape
     if in_dim != x.size(1):
         raise ValueError(f"lora_A input dim {in_dim} does not match x features {x.size(1)}")
-    tts, srt, ids, cnt, off, _, _ = metadata.as_kernel_metadata(T)
+    tts, srt, cnt, off, ids, _, _ = metadata.as_kernel_metadata(T)
     tts = _i32(tts, "token_to_slot")
     if tts is None or tts.numel() != T:
         raise RuntimeError(

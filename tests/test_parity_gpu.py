@@ -1,0 +1,357 @@
+"""Parity of the CUDA path (through the C-ABI) against the CPU oracle on identical
+seeded inputs, against the reference-generated fixtures and the reference tests'
+known answers.  Tolerance of the path: bf16 outputs within max-abs 2e-2 and rel 1e-2 of
+the fp32-accumulated oracle; rows without an adapter must keep their exact bits."""
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from helpers import assert_lora_close, build_b200_layer, load_golden
+from nanovllm_voxcpm_b200 import _native as N
+from nanovllm_voxcpm_b200 import batch_plan as BP
+from nanovllm_voxcpm_b200 import context as CTX
+from nanovllm_voxcpm_b200 import layers as L
+from nanovllm_voxcpm_b200 import lora as LORA
+from nanovllm_voxcpm_b200 import workloads as W
+from nanovllm_voxcpm_b200.lora_ops import LoRAKernelMeta, lora_expand, lora_shrink
+from oracle import lora_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(autouse=True)
+def _clean():
+    LORA.set_backend_for_testing(None)
+    CTX.reset_lora_context()
+    yield
+    N.set_option(N.OPT_CLUSTER, 0)
+    N.set_option(N.OPT_PDL, 1)
+    CTX.reset_lora_context()
+    assert N.device_status() == 0, "a kernel gave up a bounded wait"
+
+
+def metadata_for(slots: torch.Tensor, convention: str, S: int) -> LORA.LoRAMetadata:
+    """The three index conventions of the reference, built on the device."""
+    slots_cpu = slots.cpu()
+    if convention == "eager":
+        ctx = BP.build_lora_context_from_batch_plan(
+            BP.build_lora_batch_plan_from_token_to_slot({}, slots_cpu.tolist()), device=DEV
+        )
+    elif convention == "graph":
+        bufs = BP.GraphLoRABuffers.make(slots_cpu.numel() + 5, S, device=DEV)
+        bufs.load_plan(BP.build_lora_batch_plan_from_token_to_slot({}, slots_cpu.tolist()))
+        ctx = bufs.context(slots_cpu.numel())
+    elif convention == "vllm":
+        km = LoRAKernelMeta.make(S, slots_cpu.numel(), DEV)
+        km.prepare_tensors(slots_cpu.to(DEV))
+        tts, srt, cnt, off, ids, flag, n = km.meta_args(slots_cpu.numel(), specialize_active_lora=False)
+        return LORA.LoRAMetadata(tts, srt, ids, cnt, off, flag, n)
+    else:
+        raise AssertionError(convention)
+    return LORA.LoRAMetadata(ctx.token_to_slot, ctx.token_indices_sorted_by_slot, ctx.active_slot_ids,
+                             ctx.num_tokens_per_slot, ctx.slot_start_offsets, ctx.no_lora_flag, ctx.num_active_loras)
+
+
+def run_add(p: W.Projection, impl: int, convention: str = "eager", *, use_ranks=False, scaling=1.0,
+            scale_per_slot=None, y_pad=0, x_pad=0):
+    """One lora_b200_add launch on device copies of ``p``; returns (y_out, y_in) on the CPU."""
+    d = p.to_device(DEV)
+    S = d.a_slabs[0].shape[0]
+    if y_pad or x_pad:  # row-strided views into wider buffers
+        ybuf = torch.zeros(d.y.shape[0], d.y.shape[1] + y_pad, dtype=d.y.dtype, device=DEV)
+        xbuf = torch.zeros(d.x.shape[0], d.x.shape[1] + x_pad, dtype=d.x.dtype, device=DEV)
+        ybuf[:, : d.y.shape[1]] = d.y
+        xbuf[:, : d.x.shape[1]] = d.x
+        y, x = ybuf[:, : d.y.shape[1]], xbuf[:, : d.x.shape[1]]
+    else:
+        y, x = d.y.clone(), d.x
+    meta = metadata_for(d.token_to_slot, convention, S)
+    LORA.launch_add(y, x, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets, meta, scaling,
+                    rank_per_slot=d.ranks if use_ranks else None,
+                    scale_per_slot=None if scale_per_slot is None else scale_per_slot.to(DEV), impl=impl)
+    torch.cuda.synchronize()
+    return y.cpu(), p.y
+
+
+def check_against_oracle(p, out, y_in, scaling=1.0, scale_per_slot=None, what=""):
+    ref = O.add_lora(y_in, p.x, p.a_slabs, p.b_slabs, p.token_to_slot, scaling, p.col_offsets, scale_per_slot)
+    assert_lora_close(out, ref, what=what)
+    none = p.token_to_slot < 0
+    assert torch.equal(out[none].view(torch.int16), y_in[none].view(torch.int16)), f"{what}: rows without adapter changed"
+    touched = (out[~none].float() - y_in[~none].float()).abs().max() if (~none).any() else torch.tensor(1.0)
+    assert float(touched) > 0, f"{what}: no delta was applied"
+
+
+# ------------------------------------------------------------------ decode BGMV
+@pytest.mark.parametrize("convention", ["eager", "graph", "vllm"])
+@pytest.mark.parametrize("impl", [N.IMPL_GENERIC, N.IMPL_BGMV], ids=["generic", "bgmv"])
+@pytest.mark.parametrize("name", ["qkv", "o", "gate_up", "down"])
+def test_decode_projection_matches_oracle(name, impl, convention):
+    p = W.decode_projection(name, seed=7)
+    out, y_in = run_add(p, impl, convention)
+    check_against_oracle(p, out, y_in, what=f"{name}/{convention}")
+    out2, _ = run_add(p, impl, convention)
+    assert torch.equal(out.view(torch.int16), out2.view(torch.int16)), "two runs differ bitwise"
+
+
+@pytest.mark.parametrize("cluster", [1, 2, 4, 8])
+@pytest.mark.parametrize("pdl", [0, 1])
+def test_bgmv_cluster_sizes(cluster, pdl):
+    N.set_option(N.OPT_CLUSTER, cluster)
+    N.set_option(N.OPT_PDL, pdl)
+    for name in ("qkv", "down"):
+        p = W.decode_projection(name, seed=3, T=96, S=8)
+        out, y_in = run_add(p, N.IMPL_BGMV, "graph")
+        check_against_oracle(p, out, y_in, what=f"{name}/C{cluster}/pdl{pdl}")
+
+
+def test_bgmv_many_tokens_per_slot_and_single_token():
+    # 200 rows on 2 slots: up to 7 passes of 16 tokens per bucket; then a 1-row batch
+    p = W.make_projection(5, 200, 1024, [1024, 128, 128], 2, 32, p_none=0.2)
+    out, y_in = run_add(p, N.IMPL_BGMV)
+    check_against_oracle(p, out, y_in, what="many tokens")
+    p1 = W.make_projection(6, 1, 1024, [1024], 4, 32, token_to_slot=[3])
+    out, y_in = run_add(p1, N.IMPL_BGMV)
+    check_against_oracle(p1, out, y_in, what="one token")
+
+
+def test_bgmv_mixed_ranks_scales_and_strides():
+    ranks = [(8, 16, 64)[s % 3] for s in range(6)]
+    p = W.make_projection(9, 70, 2048, [2048, 256, 256], 6, 64, ranks=ranks, p_none=0.15)
+    sps = torch.tensor([1.0, 0.5, 2.0, 1.5, 0.25, 1.0])
+    for use_ranks in (False, True):
+        out, y_in = run_add(p, N.IMPL_BGMV, "graph", use_ranks=use_ranks, scaling=0.5, scale_per_slot=sps,
+                            y_pad=24, x_pad=8)
+        check_against_oracle(p, out, y_in, 0.5, sps, what=f"ranks={use_ranks}")
+    # per-slot rank 0 = empty slot: exact zero delta for its rows
+    p.ranks[2] = 0
+    p.a_slabs = [a.clone() for a in p.a_slabs]
+    p.b_slabs = [b.clone() for b in p.b_slabs]
+    for a, b in zip(p.a_slabs, p.b_slabs):
+        a[2].zero_()
+        b[2].zero_()
+    out, y_in = run_add(p, N.IMPL_BGMV, use_ranks=True)
+    rows = p.token_to_slot == 2
+    assert rows.any() and torch.equal(out[rows], y_in[rows])
+    check_against_oracle(p, out, y_in, what="empty slot")
+
+
+def test_zero_width_slice_and_auto_dispatch():
+    p = W.make_projection(4, 40, 1024, [512, 0, 256], 4, 32)
+    p.a_slabs[1] = p.a_slabs[0]  # never read
+    for impl in (N.IMPL_AUTO, N.IMPL_GENERIC, N.IMPL_BGMV):
+        out, y_in = run_add(p, impl)
+        check_against_oracle(p, out, y_in, what=f"impl {impl}")
+
+
+def test_unsupported_shapes_are_reported_not_launched():
+    p = W.make_projection(4, 8, 1000, [64], 2, 16)  # in % 32 != 0, r % 32 != 0
+    with pytest.raises(RuntimeError, match="fused decode kernel"):
+        run_add(p, N.IMPL_BGMV)
+    out, y_in = run_add(p, N.IMPL_AUTO)  # auto falls back to the generic kernel
+    check_against_oracle(p, out, y_in, what="auto->generic")
+
+
+# --------------------------------------------------------------- config 1 / dtypes
+def test_config1_matches_reference_fixture():
+    g = load_golden("config1.npz")
+    p = W.config1(0)
+    out, y_in = run_add(p, N.IMPL_AUTO)
+    assert_lora_close(out, torch.from_numpy(g["y"]), what="config1 vs reference fixture")
+    check_against_oracle(p, out, y_in, what="config1")
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.float16, 2e-2)])
+def test_generic_kernel_other_dtypes(dtype, tol):
+    p = W.make_projection(21, 33, 160, [48, 24], 3, 8, dtype=dtype, p_none=0.3)
+    d = p.to_device(DEV)
+    y = d.y.clone()
+    LORA.launch_add(y, d.x, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets,
+                    metadata_for(d.token_to_slot, "eager", 3), 0.5, impl=N.IMPL_AUTO)
+    ref = O.add_lora(p.y, p.x, p.a_slabs, p.b_slabs, p.token_to_slot, 0.5, p.col_offsets)
+    assert_lora_close(y, ref, max_abs=tol, what=str(dtype))
+    none = p.token_to_slot < 0
+    assert torch.equal(y.cpu()[none], p.y[none])
+
+
+def test_shrink_and_expand_ops_match_oracle():
+    """Raw ops with the reference's positional signature and vLLM-style metadata
+    (tests/unit/test_lora_cuda.py:836-911)."""
+    dtype = torch.float16
+    g = torch.Generator().manual_seed(2)
+    x = (torch.arange(4 * 160, dtype=torch.float32).reshape(4, 160) / 100).to(dtype)
+    a = torch.randn(2, 8, 160, generator=g).to(dtype)
+    slots = torch.tensor([0, 1, 0, 1], dtype=torch.int32)
+    meta = (slots.to(DEV), torch.tensor([0, 2, 1, 3], dtype=torch.int32, device=DEV),
+            torch.tensor([2, 2, 0], dtype=torch.int32, device=DEV), torch.tensor([0, 2, 4, 4], dtype=torch.int32, device=DEV),
+            torch.tensor([0, 1, -1], dtype=torch.int32, device=DEV), False, 2)
+    out = torch.empty((1, 4, 8), device=DEV, dtype=dtype)
+    lora_shrink(x.to(DEV), [a.to(DEV)], out, *meta, 0.5)
+    assert_lora_close(out, O.shrink(x, [a], slots, 0.5), max_abs=5e-2, rel=5e-2)
+
+    # bf16, two slices, fp32 intermediate (the row-parallel [T, r] exchange format)
+    p = W.make_projection(31, 50, 256, [64, 32], 4, 16, p_none=0.2)
+    d = p.to_device(DEV)
+    meta = (d.token_to_slot, None, None, None, None, False, 0)
+    tmp32 = torch.empty((2, 50, 16), device=DEV, dtype=torch.float32)
+    lora_shrink(d.x, d.a_slabs, tmp32, *meta, 1.0)
+    ref_tmp = O.shrink(p.x, p.a_slabs, p.token_to_slot)
+    torch.testing.assert_close(tmp32.cpu(), ref_tmp, atol=1e-4, rtol=1e-4)
+    assert not tmp32.cpu()[:, p.token_to_slot < 0].any()  # zero rows without adapter
+    y = d.y.clone()
+    lora_expand(tmp32, d.b_slabs, y, *meta, offset_start=0, add_inputs=True)
+    assert_lora_close(y, O.expand(p.y, ref_tmp, p.b_slabs, p.token_to_slot))
+    y2 = torch.zeros_like(d.y)
+    lora_expand(tmp32[1:].contiguous(), d.b_slabs[1:], y2, *meta, offset_start=64, add_inputs=False)
+    ref2 = O.expand(torch.zeros_like(p.y), ref_tmp[1:], p.b_slabs[1:], p.token_to_slot, 64, False)
+    assert_lora_close(y2, ref2)
+    assert not y2.cpu()[:, :64].any()
+
+
+# ------------------------------------------------------ backend protocol / layers
+def test_backend_add_lora_contract():
+    """tests/unit/test_lora_cuda.py:804-833 (fp16, scaling 0.5 -> [4, 10]) and the
+    in-place / fresh-buffer rules of lora.py:276-289."""
+    be = LORA.B200LoRABackend()
+    assert be.availability().available
+    y = torch.zeros(2, 1, device=DEV, dtype=torch.float16)
+    x = torch.tensor([[2.0, 3.0], [5.0, 7.0]], device=DEV, dtype=torch.float16)
+    meta = LORA.LoRAMetadata(torch.zeros(2, dtype=torch.int32, device=DEV), torch.arange(2, dtype=torch.int32, device=DEV),
+                             torch.tensor([0], dtype=torch.int32, device=DEV), torch.tensor([2], dtype=torch.int32, device=DEV),
+                             torch.tensor([0, 2], dtype=torch.int32, device=DEV), False, 1)
+    out = be.add_lora([y], x, [torch.tensor([[[1.0, 0.0]]], device=DEV, dtype=torch.float16)],
+                      [torch.tensor([[[4.0]]], device=DEV, dtype=torch.float16)],
+                      indices=torch.zeros(2, dtype=torch.long, device=DEV), metadata=meta, scaling=0.5)[0]
+    assert out.data_ptr() == y.data_ptr() and out.cpu().flatten().tolist() == [4.0, 10.0]
+
+    p = W.make_projection(8, 24, 1024, [256, 128], 4, 32).to_device(DEV)
+    m = metadata_for(p.token_to_slot, "eager", 4)
+    parts = list(p.y.split(p.out_sizes, dim=-1))
+    before = p.y.clone()
+    fresh = be.add_lora(parts, p.x, p.a_slabs, p.b_slabs, indices=p.token_to_slot, metadata=m, scaling=1.0)
+    assert torch.equal(p.y, before), "inputs must stay untouched without y_packed"
+    packed = p.y.clone()
+    same = be.add_lora(list(packed.split(p.out_sizes, dim=-1)), p.x, p.a_slabs, p.b_slabs, indices=p.token_to_slot,
+                       metadata=m, scaling=1.0, y_packed=packed)
+    assert same[0].data_ptr() == packed.data_ptr()
+    assert torch.equal(torch.cat(fresh, -1), packed)
+    ref = O.add_lora(before, p.x, p.a_slabs, p.b_slabs, p.token_to_slot.cpu())
+    assert_lora_close(packed, ref)
+    # single-adapter helpers of the protocol
+    a1, b1 = p.a_slabs[0][1], p.b_slabs[0][1]
+    h = be.shrink(p.x, a1)
+    assert_lora_close(h, p.x.float().cpu() @ a1.float().cpu().T)
+    e = be.expand(h, b1, scaling=0.5)
+    assert_lora_close(e, (h.float().cpu() @ b1.float().cpu().T) * 0.5)
+
+
+@pytest.mark.parametrize("case", cases.LAYER_CASES, ids=lambda c: c["name"])
+def test_layers_match_reference_fixture_fp32(case):
+    g = load_golden("layers.npz")
+    inputs = cases.build_inputs(case)
+    saved = L.dist.all_reduce
+    L.dist.all_reduce = lambda t, *a, **k: t
+    try:
+        for rank in range(case.get("tp", 1)):
+            layer, x = build_b200_layer(L, case, inputs, rank, dtype=torch.float32, device=DEV)
+            CTX.set_lora_context(CTX.build_lora_context_from_token_to_slot(inputs["slots"].to(DEV)))
+            with torch.no_grad():
+                y = layer(x)
+            torch.testing.assert_close(y.cpu(), torch.from_numpy(g[f"{case['name']}/y_rank{rank}"]), atol=2e-4, rtol=1e-4)
+            CTX.reset_lora_context()
+            with torch.no_grad():
+                base = layer(x)
+            none = inputs["slots"] < 0
+            assert torch.equal(y.cpu()[none], base.cpu()[none])
+    finally:
+        L.dist.all_reduce = saved
+        L._get_world_size = lambda: 1
+        L._get_rank = lambda: 0
+
+
+def test_kat_layers_on_device():
+    """tests/unit/test_lora_cuda.py:135-189 and :576-615 through this package's layers."""
+    layer = L.LoRALinear(3, 2, bias=False, max_loras=2, max_lora_rank=4).to(DEV)
+    layer.weight.data.zero_()
+    layer.set_slot_lora(0, torch.tensor([[1.0, 0, 0], [0, 1.0, 0]], device=DEV), torch.tensor([[1.0, 0], [0, 1.0]], device=DEV), 2, 1.0)
+    layer.set_slot_lora(1, torch.tensor([[0, 0, 1.0]], device=DEV), torch.tensor([[2.0], [4.0]], device=DEV), 1, 0.25)
+    x = torch.tensor([[2.0, 3.0, 5.0], [7.0, 11.0, 13.0], [17.0, 19.0, 23.0]], device=DEV)
+    assert not layer(x).any()
+    CTX.set_lora_context(CTX.LoRAContext(
+        token_to_slot=torch.tensor([0, -1, 1], dtype=torch.int32, device=DEV),
+        token_indices_sorted_by_slot=torch.tensor([0, 2, 1], dtype=torch.int32, device=DEV),
+        active_slot_ids=torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+        num_tokens_per_slot=torch.tensor([1, 1], dtype=torch.int32, device=DEV),
+        slot_start_offsets=torch.tensor([0, 1, 2], dtype=torch.int32, device=DEV), no_lora_flag=False))
+    assert layer(x).cpu().tolist() == [[2.0, 3.0], [0.0, 0.0], [11.5, 23.0]]
+
+    merged = L.LoRAMergedColumnParallelLinear(2, [1, 1], lora_targets=[0], max_loras=1, max_lora_rank=1).to(DEV).half()
+    merged.weight.data.zero_()
+    merged.set_slot_lora(0, torch.tensor([[[1.0, 0.0]]], device=DEV, dtype=torch.float16),
+                         [torch.tensor([[2.0]], device=DEV, dtype=torch.float16)], 1, 0.5)
+    CTX.set_lora_context(CTX.build_lora_context_from_token_to_slot(torch.tensor([0], dtype=torch.int32, device=DEV)))
+    assert merged(torch.tensor([[4.0, 8.0]], device=DEV, dtype=torch.float16)).cpu().tolist() == [[4.0, 0.0]]
+
+
+def test_context_length_mismatch_raises_before_launch():
+    layer = L.LoRALinear(32, 32, bias=False, max_loras=1, max_lora_rank=32).to(DEV).bfloat16()
+    layer.set_slot_lora(0, torch.ones(32, 32, device=DEV), torch.ones(32, 32, device=DEV), 32, 1.0)
+    CTX.set_lora_context(CTX.build_lora_context_from_token_to_slot(torch.zeros(3, dtype=torch.int32, device=DEV)))
+    with pytest.raises(RuntimeError, match="length does not match"):
+        layer(torch.ones(2, 32, device=DEV, dtype=torch.bfloat16))
+
+
+# ------------------------------------------------------------------- CUDA graphs
+def test_cuda_graph_replay_with_changing_slots_and_weights():
+    """Graph contract of the runner (engine/model_runner.py:819-923): fixed grid over
+    max_loras+1 buckets, metadata and slab contents change between capture and replay
+    (tests/unit/test_lora_cuda.py:224-382,454-532)."""
+    S, T = 8, 32
+    layer = L.LoRAQKVParallelLinear(1024, 64, 16, 2, max_loras=S, max_lora_rank=32).to(DEV).bfloat16()
+    g = torch.Generator().manual_seed(1)
+    layer.weight.data.copy_(torch.randn(1280, 1024, generator=g) * 0.02)
+
+    def load(slot, seed, rank):
+        gg = torch.Generator().manual_seed(seed)
+        a = (torch.randn(3, rank, 1024, generator=gg) * 0.05).to(DEV)
+        b = [(torch.randn(w, rank, generator=gg) * 0.05).to(DEV) for w in (1024, 128, 128)]
+        layer.set_slot_lora(slot, a, b, rank, 1.0)
+
+    for s in range(S):
+        load(s, 100 + s, 32)
+    bufs = BP.GraphLoRABuffers.make(T, S, device=DEV)
+    x = torch.zeros(T, 1024, device=DEV, dtype=torch.bfloat16)
+    out = torch.zeros(T, 1280, device=DEV, dtype=torch.bfloat16)
+    bufs.load_plan(BP.build_lora_batch_plan_from_token_to_slot({}, [0] * T))  # capture with every row on slot 0
+    CTX.set_lora_context(bufs.context(T))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side), torch.no_grad():
+        layer(x)  # warm-up outside capture
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.no_grad(), torch.cuda.graph(graph):
+        out.copy_(layer(x))
+
+    def eager_reference(slots, xin):
+        CTX.set_lora_context(BP.build_lora_context_from_slot_list(slots, device=DEV))
+        with torch.no_grad():
+            return layer(xin).clone()
+
+    for step, slots in enumerate([[(i * 3) % S if i % 5 else -1 for i in range(T)], [-1] * T, [S - 1] * T]):
+        if step == 2:
+            load(S - 1, 999, 16)  # slot rewritten between capture and replay
+        x.copy_((torch.randn(T, 1024, generator=g)).to(torch.bfloat16))
+        bufs.load_plan(BP.build_lora_batch_plan_from_token_to_slot({}, slots))
+        graph.replay()
+        torch.cuda.synchronize()
+        want = eager_reference(slots, x)
+        assert torch.equal(out, want), f"graph replay differs from eager at step {step}"
+        a_slabs = [layer.lora_A.data[i].cpu() for i in range(3)]
+        b_slabs = [getattr(layer, f"lora_B_{t}").data.cpu() for t in "qkv"]
+        base = (x.float().cpu() @ layer.weight.data.float().cpu().T).to(torch.bfloat16)
+        ref = O.add_lora(base, x.cpu(), a_slabs, b_slabs, slots, 1.0, [0, 1024, 1152])
+        assert_lora_close(out, ref, max_abs=4e-2, what=f"graph step {step}")  # base GEMM rounding included
