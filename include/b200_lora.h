@@ -132,6 +132,7 @@ int lora_b200_expand(void* y, int64_t y_ld, const void* tmp, int32_t tmp_dtype, 
 /* Tuning knobs of the fused decode kernel (process-wide, read at launch time). */
 #define B200_LORA_OPT_CLUSTER 1 /* CTAs per slot bucket: 1, 2, 4, 8; 0 = choose from n_buckets */
 #define B200_LORA_OPT_PDL 2     /* 1 = launch with programmatic stream serialization (default), 0 = off */
+#define B200_LORA_OPT_RING_KB 3 /* cap of the shared-memory stage ring in KB, 0 = as large as fits */
 
 /* Sets a tuning knob; returns 0, or B200_LORA_EINVAL for an unknown key / value.
  * No counterpart in the reference (its tile configs are static tables,

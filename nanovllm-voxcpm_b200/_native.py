@@ -15,7 +15,8 @@ from ctypes import POINTER, c_char_p, c_float, c_int32, c_int64, c_size_t, c_voi
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libb200lora.so")
+#: B200_LORA_LIB points at another build of the same ABI (e.g. an instrumented one)
+LIB_PATH = os.environ.get("B200_LORA_LIB") or os.path.join(_HERE, "lib", "libb200lora.so")
 
 ABI_VERSION = 1
 
@@ -51,7 +52,7 @@ _SIGNATURES = {
     "lora_b200_device_status": (c_int32, [POINTER(c_int32), c_int32]),
 }
 
-OPT_CLUSTER, OPT_PDL = 1, 2
+OPT_CLUSTER, OPT_PDL, OPT_RING_KB = 1, 2, 3
 
 
 class NativeLibraryError(RuntimeError):

@@ -89,8 +89,21 @@ int lora_b200_set_option(int32_t key, int32_t value) {
     bgmv_options().pdl = value != 0;
     return B200_LORA_OK;
   }
+  if (key == B200_LORA_OPT_RING_KB) {
+    if (value < 0 || value > 227) return fail(B200_LORA_EINVAL, "ring size %d KB outside [0, 227]", value);
+    bgmv_options().ring_kb = value;
+    return B200_LORA_OK;
+  }
   return fail(B200_LORA_EINVAL, "unknown option %d", key);
 }
+
+#ifdef B200_TRACE
+// Tuning builds only: copies the phase timeline of the last fused-decode launch.
+int lora_b200_debug_trace(long long* out, int32_t n_values) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_b200_trace, sizeof(long long) * (size_t)n_values);
+  return e == cudaSuccess ? 0 : B200_LORA_ECUDA;
+}
+#endif
 
 int lora_b200_device_status(int32_t* status, int32_t reset) {
   if (status == nullptr) return fail(B200_LORA_EINVAL, "null status pointer");

@@ -9,22 +9,25 @@
 //     shrink : the n*r stacked rank rows are split across the C CTAs (full K each)
 //     expand : each slice's output rows are split across the C CTAs
 //   and the rank-r intermediate tmp[16 tokens, n*r] (bf16) is all-gathered through
-//   distributed shared memory between the two phases.
+//   distributed shared memory between the two phases (stores into every peer's buffer,
+//   then one remote mbarrier arrive per peer; the buffer is double-buffered by pass).
 //
-// Data movement
-//   All weight and activation rows reach shared memory through 1-D bulk async copies
-//   (cp.async.bulk, the TMA unit) into a ring of stages guarded by full/empty
-//   mbarriers; warp 0 issues the copies NS-1 tiles ahead, so at kernel start the
-//   CTA's first NS tiles (usually all of its weights) are in flight at once. The
-//   weights do not depend on the previous kernel in the stream, so with programmatic
-//   dependent launch their copies are issued before griddepcontrol.wait.
-//
-// Math
-//   mma.sync m16n8k16 bf16 -> fp32 with tokens as the 16-row operand (a pass handles
-//   16 tokens of the bucket) and weight rows as the 8-column operand. Fragments are
-//   read as 16-byte vectors: thread (g,t) of a warp takes columns [8t, 8t+8) of a
-//   32-column block for both operands, which is a fixed permutation of the k index
-//   shared by A and B and therefore leaves the dot products unchanged.
+// Roles
+//   warp 8      producer: walks the CTA's tile list and issues 1-D bulk async copies
+//               (cp.async.bulk, the TMA unit) into a ring of stages guarded by full/empty
+//               mbarriers. A shrink tile is 8 rank rows x up to 1024 columns (one 16 KB
+//               copy when the rows are contiguous, else 8 row copies), an expand tile is
+//               one contiguous copy of up to 16 KB of lora_B rows. The weights do not
+//               depend on the previous kernel of the stream, so under programmatic
+//               dependent launch they are requested before griddepcontrol.wait.
+//   warps 0-7   consumers: mma.sync m16n8k16 bf16 -> fp32 with tokens as the 16-row
+//               operand (a pass handles 16 tokens of the bucket) and weight rows as the
+//               8-column operand. Activations are read straight into MMA fragments
+//               (16-byte global loads, once per 1024-column part); y is read one tile
+//               ahead and written back with 16-byte stores.
+//   Fragments are read as 16-byte vectors: thread (g,t) of a warp takes columns
+//   [8t, 8t+8) of a 32-column block for both operands, which is a fixed permutation of the
+//   k index shared by A and B and therefore leaves the dot products unchanged.
 //
 // Rows whose slot is -1 are in no bucket and are never read or written.
 #pragma once
@@ -34,17 +37,31 @@
 
 namespace b200lora {
 
-constexpr int kBgmvWarps = 8;
-constexpr int kBgmvThreads = kBgmvWarps * 32;
-constexpr int kBgmvTok = 16;            // tokens per pass (one MMA M tile)
-constexpr int kBgmvMaxRc = 48;          // stacked rank rows per CTA
-constexpr int kBgmvStageMax = 40 * 1024;
-constexpr int kBgmvSmemMax = 232448;    // 227 KB opt-in maximum per CTA
+constexpr int kBgmvWarps = 8;                       // consumer warps
+constexpr int kBgmvConsumers = kBgmvWarps * 32;
+constexpr int kBgmvThreads = kBgmvConsumers + 32;   // + producer warp
+constexpr int kBgmvTok = 16;           // tokens per pass (one MMA M tile)
+constexpr int kBgmvMaxRc = 64;         // stacked rank rows per CTA
+constexpr int kBgmvKP = 1024;          // columns per shrink tile
+constexpr int kBgmvXBlocks = kBgmvKP / 32 / kBgmvWarps;  // 32-column blocks per warp and tile
+constexpr int kBgmvSmemMax = 232448;   // 227 KB opt-in maximum per CTA
+constexpr int kBgmvMaxStages = 12;
 
 // status bits of the device status word
 constexpr int kStatusWaitGaveUp = 1;
 
 __device__ int g_b200_status = 0;
+
+// Optional phase timeline (SM clock) of rank-0 CTAs, compiled in only for tuning builds.
+#ifdef B200_TRACE
+__device__ long long g_b200_trace[1024 * 32];
+#define B200_TRACE_AT(i, who) \
+  if (tid == (who) && c == 0 && blockIdx.y < 1024) g_b200_trace[blockIdx.y * 32 + (i)] = clock64();
+#else
+#define B200_TRACE_AT(i, who)
+#endif
+#define B200_TRACE_POINT(i) B200_TRACE_AT(i, 0)
+#define B200_TRACE_PRODUCER(i) B200_TRACE_AT(i, kBgmvConsumers)
 
 struct BgmvProblem {
   void* y; int64_t y_ld; const void* x; int64_t x_ld;
@@ -62,13 +79,15 @@ struct BgmvParams {
   const int32_t* rank_per_slot; const float* scale_per_slot;
   const int32_t *sorted_idx, *slot_ids, *counts, *offsets;
   int n_buckets; float scaling;
-  int C;            // cluster size
-  int KC;           // shrink K chunk per tile (256 or 512)
-  int pitchA;       // bytes between rows of a shrink tile (KC*2 + 64)
-  int ER;           // out rows per expand tile (multiple of 32)
+  int c_shift;      // cluster size C = 1 << c_shift
+  int KP, nkp;      // columns per shrink tile (min(in, 1024)) and number of K parts
+  int pitchA;       // bytes between rows of a shrink tile (KP*2, +64 when rows are copied one by one)
+  int ER, er_shift; // out rows per expand tile (power of two, 32..256)
+  int oc[B200_LORA_MAX_SLICES];  // out rows of each slice owned by one CTA (multiple of 32)
   int stage_bytes, NS;
   int red_pitch;    // floats per token row of the cross-warp reduction buffer
   int pitchT;       // bytes per token row of tmp
+  int tmp_bytes;    // bytes of one tmp buffer
   int off_red, off_tmp, off_bar;
   int use_pdl;
 };
@@ -76,33 +95,68 @@ struct BgmvParams {
 __host__ __device__ __forceinline__ int ceil_div_i(int a, int b) { return (a + b - 1) / b; }
 __host__ __device__ __forceinline__ int round_up_i(int a, int b) { return ceil_div_i(a, b) * b; }
 
-__global__ void __launch_bounds__(kBgmvThreads, 1) bgmv_fused_kernel(const __grid_constant__ BgmvParams p) {
+#ifndef BGMV_MINBLOCKS
+#define BGMV_MINBLOCKS 1
+#endif
+#ifndef BGMV_YDEPTH
+#define BGMV_YDEPTH 2
+#endif
+__global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kernel(const __grid_constant__ BgmvParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int bucket = blockIdx.y;
-  const int C = p.C;
+  const int C = 1 << p.c_shift;
   const int c = (int)cluster_ctarank();
+  const int NS = p.NS;
 
-  // ---- bucket metadata (uniform across the cluster) -------------------------
+  B200_TRACE_POINT(0)
+  // Let the next launch of the stream start at once: before its own griddepcontrol.wait it only
+  // reads index metadata and lora slabs, which no kernel of this library writes, so its weight
+  // traffic overlaps this kernel's compute and keeps HBM busy across launch boundaries.
+  if (p.use_pdl) griddep_launch_dependents();
+  // ---- bucket metadata (uniform across the cluster); barrier set-up overlaps the loads
   const int slot = p.slot_ids[bucket];
   const int cnt = p.counts[bucket];
   const int start = p.offsets[bucket];
+
+  float* red = reinterpret_cast<float*>(smem + p.off_red);
+  uint8_t* tmp_base = smem + p.off_tmp;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_bar);  // full[], empty[], tmp_ready[2]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kBgmvMaxStages + 2);
+  const uint32_t bar_base = smem_u32(bars);
+  const uint32_t ring_base = smem_u32(smem);
+  // one barrier per tmp buffer: pass p uses barrier p & 1 in phase (p >> 1) & 1
+  const uint32_t tmp_ready_bars = bar_base + 8u * (uint32_t)(2 * kBgmvMaxStages);
+  auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(kBgmvMaxStages + s); };
+  if (tid < NS) {
+    mbar_init(full_bar(tid), 1);
+    mbar_init(empty_bar(tid), kBgmvWarps);
+    if (tid == 0) {
+      mbar_init(tmp_ready_bars, (uint32_t)C);
+      mbar_init(tmp_ready_bars + 8u, (uint32_t)C);
+      *abort_flag = 0;
+    }
+    mbar_fence_init();
+  }
+
   if (slot < 0 || slot >= p.S || cnt <= 0 || start < 0 || start > p.T - cnt) return;
   int rank = p.r_max;
   if (p.rank_per_slot != nullptr) rank = min(max(p.rank_per_slot[slot], 0), p.r_max);
   const int r_eff = min(p.r_max, (rank + 31) & ~31);
   if (r_eff == 0) return;
   const float sc = p.scaling * (p.scale_per_slot != nullptr ? p.scale_per_slot[slot] : 1.0f);
+  B200_TRACE_POINT(1)
 
   const int n = p.st.n;
   const int in_dim = p.in_dim;
-  const int Q = n * r_eff;                                  // stacked rank rows
-  const int Rc = round_up_i(ceil_div_i(Q, C), 8);           // rows owned per CTA
+  const int Q = n * r_eff;                                       // stacked rank rows
+  const int Rc = ((((Q + C - 1) >> p.c_shift) + 7) & ~7);        // rows owned per CTA
   const int q_lo = min(c * Rc, Q);
-  const int rows_c = min(q_lo + Rc, Q) - q_lo;              // multiple of 8, may be 0
-  const int nt_c = rows_c >> 3;                             // 8-row MMA column tiles
-  const int KC = p.KC, pitchA = p.pitchA, ER = p.ER;
-  const int nkt_c = rows_c > 0 ? ceil_div_i(in_dim, KC) : 0;
+  const int rows_c = min(q_lo + Rc, Q) - q_lo;                   // multiple of 8, may be 0
+  const int nt_c = rows_c >> 3;                                  // 8-row tiles of this CTA
+  const int KP = p.KP, pitchA = p.pitchA, ER = p.ER, nkp = p.nkp;
+  const int shrink_tiles = nt_c * nkp;
   int e_lo[B200_LORA_MAX_SLICES], e_n[B200_LORA_MAX_SLICES], e_tiles[B200_LORA_MAX_SLICES];
   int tiles_exp = 0;
 #pragma unroll
@@ -110,170 +164,250 @@ __global__ void __launch_bounds__(kBgmvThreads, 1) bgmv_fused_kernel(const __gri
     e_lo[s] = e_n[s] = e_tiles[s] = 0;
     if (s < n) {
       const int out = p.st.out[s];
-      const int Oc = round_up_i(ceil_div_i(out, C), 32);
-      e_lo[s] = min(c * Oc, out);
-      e_n[s] = min(e_lo[s] + Oc, out) - e_lo[s];
-      e_tiles[s] = ceil_div_i(e_n[s], ER);
+      e_lo[s] = min(c * p.oc[s], out);
+      e_n[s] = min(e_lo[s] + p.oc[s], out) - e_lo[s];
+      e_tiles[s] = (e_n[s] + ER - 1) >> p.er_shift;
       tiles_exp += e_tiles[s];
     }
   }
-  const int tpp = nkt_c + tiles_exp;  // tiles per pass
-  const int npass = ceil_div_i(cnt, kBgmvTok);
-  const int total = tpp * npass;
-  const int NS = p.NS;
+  const int npass = (cnt + kBgmvTok - 1) >> 4;
+  const int total = (shrink_tiles + tiles_exp) * npass;
 
-  uint8_t* ring = smem;
-  float* red = reinterpret_cast<float*>(smem + p.off_red);
-  uint8_t* tmp_full = smem + p.off_tmp;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_bar);  // full[NS], empty[NS]
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * NS);
-  const uint32_t bar_base = smem_u32(bars);
-  auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(NS + s); };
+  __syncthreads();  // barriers initialised
+  B200_TRACE_POINT(2)
+  // Start-up cluster barrier: every CTA of the cluster has initialised its barriers once it
+  // completes. Consumers wait on it before their first remote store, the producer before it exits.
+  cluster_arrive();
 
-  if (tid == 0) {
-    for (int s = 0; s < NS; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), kBgmvWarps);
-    }
-    *abort_flag = 0;
-    mbar_fence_init();
-    fence_proxy_async_smem();
-  }
-  __syncthreads();
-  cluster_arrive();  // peers are running once this completes (waited before the first remote store)
-
-  // ---- tile issue (warp 0) -----------------------------------------------------
-  // part bit 0: weight rows, bit 1: activation rows. A shrink tile's full barrier
-  // takes expect_tx for the weights and arrive.expect_tx for the activations, so the
-  // two halves may be issued at different times.
-  auto issue_tile = [&](int it, int part) {
-    const int stage = it % NS;
-    const uint32_t sbase = smem_u32(ring + (size_t)stage * p.stage_bytes);
-    const uint32_t fb = full_bar(stage);
-    const int pass = it / tpp;
-    int li = it - pass * tpp;
-    if (li < nkt_c) {
-      const int k0 = li * KC;
-      const uint32_t row_bytes = (uint32_t)min(KC, in_dim - k0) * 2u;
-      const int ntok = min(kBgmvTok, cnt - pass * kBgmvTok);
-      if (part & 1) {
-        if (lane == 0) mbar_expect_tx(fb, (uint32_t)rows_c * row_bytes);
-        __syncwarp();
-        for (int i = lane; i < rows_c; i += 32) {
-          const int q = q_lo + i;
-          const int s = q / r_eff, j = q - s * r_eff;
-          const __nv_bfloat16* src =
-              static_cast<const __nv_bfloat16*>(p.st.a[s]) + ((int64_t)slot * p.r_max + j) * in_dim + k0;
-          bulk_g2s(sbase + (uint32_t)(i * pitchA), src, row_bytes, fb);
-        }
-      }
-      if (part & 2) {
-        if (lane == 0) mbar_arrive_expect_tx(fb, (uint32_t)ntok * row_bytes);
-        __syncwarp();
-        for (int i = lane; i < ntok; i += 32) {
-          int tok = p.sorted_idx[start + pass * kBgmvTok + i];
-          tok = min(max(tok, 0), p.T - 1);
-          bulk_g2s(sbase + (uint32_t)((rows_c + i) * pitchA), p.x + (int64_t)tok * p.x_ld + k0, row_bytes, fb);
-        }
-      }
-    } else if (part & 1) {
-      li -= nkt_c;
-      int s_sel = 0;
+  if (warp == kBgmvWarps) {
+    // =========================== producer warp ===========================
+    int i_shrink = shrink_tiles > 0 ? 1 : 0, i_kp = 0, i_j = 0;  // cursor: phase, K part, 8-row tile
+    int i_s = 0, i_et = 0;                                       // cursor: slice / tile in slice
+    int i_qs = 0, i_qr = q_lo;                                   // slice / row of the cursor's first rank row
+    while (i_qr >= r_eff) { i_qr -= r_eff; ++i_qs; }
+    const int q0_s = i_qs, q0_r = i_qr;
+    int p_stage = 0, p_round = 0;
+    const int npro = min(NS, total);
+    for (int it = 0; it < total; ++it) {
+      if (p_round > 0) mbar_wait_bounded(empty_bar(p_stage), (uint32_t)((p_round & 1) ^ 1), abort_flag);
+      const uint32_t sbase = ring_base + (uint32_t)p_stage * (uint32_t)p.stage_bytes;
+      const uint32_t fb = full_bar(p_stage);
+      if (i_shrink) {
+        const int k0 = i_kp * KP;
+        const uint32_t row_bytes = (uint32_t)min(KP, in_dim - k0) * 2u;
+        const void* aptr = nullptr;
 #pragma unroll
-      for (int s = 0; s < B200_LORA_MAX_SLICES - 1; ++s) {
-        if (s_sel == s && li >= e_tiles[s]) { li -= e_tiles[s]; s_sel = s + 1; }
-      }
-      int lo = 0, en = 0, out = 0;
-      const void* bptr = nullptr;
-#pragma unroll
-      for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) {
-        if (s == s_sel) { lo = e_lo[s]; en = e_n[s]; out = p.st.out[s]; bptr = p.st.b[s]; }
-      }
-      const int r0 = li * ER;
-      const int nrows = min(ER, en - r0);
-      if (lane == 0) {
-        const uint32_t bytes = (uint32_t)nrows * (uint32_t)p.r_max * 2u;
-        mbar_arrive_expect_tx(fb, bytes);
+        for (int s = 0; s < B200_LORA_MAX_SLICES; ++s)
+          if (s == i_qs) aptr = p.st.a[s];
         const __nv_bfloat16* src =
-            static_cast<const __nv_bfloat16*>(bptr) + ((int64_t)slot * out + lo + r0) * p.r_max;
-        bulk_g2s(sbase, src, bytes, fb);
-      }
-    }
-    __syncwarp();
-  };
-
-  // ---- prologue: weights first (independent of the previous kernel) ----------------
-  const int npro = min(NS, total);
-  if (warp == 0) {
-    for (int it = 0; it < npro; ++it) issue_tile(it, 1);
-  }
-  if (p.use_pdl) {
-    griddep_wait();
-    griddep_launch_dependents();
-  }
-  if (warp == 0) {
-    for (int it = 0; it < npro; ++it) issue_tile(it, 2);
-  }
-
-  int it = 0;  // global tile counter, identical in every thread
-  for (int pass = 0; pass < npass; ++pass) {
-    const bool valid_lo = pass * kBgmvTok + g < cnt;
-    const bool valid_hi = pass * kBgmvTok + g + 8 < cnt;
-
-    // ===== shrink: acc[j] = x[16 tok, K slice of this warp] . A_rows[8j..8j+8)^T =====
-    float acc[kBgmvMaxRc / 8][4];
-#pragma unroll
-    for (int j = 0; j < kBgmvMaxRc / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-
-    for (int kt = 0; kt < nkt_c; ++kt, ++it) {
-      const int stage = it % NS;
-      // refill the stage freed by the previous tile
-      if (warp == 0 && it >= 1 && it - 1 + NS < total) {
-        const int prev = it - 1;
-        mbar_wait_bounded(empty_bar(prev % NS), (uint32_t)((prev / NS) & 1), abort_flag);
-        issue_tile(prev + NS, 3);
-      }
-      mbar_wait_bounded(full_bar(stage), (uint32_t)((it / NS) & 1), abort_flag);
-      const uint32_t sbase = smem_u32(ring + (size_t)stage * p.stage_bytes);
-      const int k0 = kt * KC;
-      const int nblk = min(KC, in_dim - k0) >> 5;  // 32-column blocks in this tile
-      for (int b = warp; b < nblk; b += kBgmvWarps) {
-        const uint32_t coff = (uint32_t)(b * 32 + t * 8) * 2u;
-        uint4 xlo = make_uint4(0, 0, 0, 0), xhi = make_uint4(0, 0, 0, 0);
-        if (valid_lo) xlo = lds128(sbase + (uint32_t)((rows_c + g) * pitchA) + coff);
-        if (valid_hi) xhi = lds128(sbase + (uint32_t)((rows_c + g + 8) * pitchA) + coff);
-#pragma unroll
-        for (int j = 0; j < kBgmvMaxRc / 8; ++j) {
-          if (j < nt_c) {
-            const uint4 w = lds128(sbase + (uint32_t)((8 * j + g) * pitchA) + coff);
-            mma_bf16_16816(acc[j], xlo.x, xhi.x, xlo.y, xhi.y, w.x, w.y);
-            mma_bf16_16816(acc[j], xlo.z, xhi.z, xlo.w, xhi.w, w.z, w.w);
+            static_cast<const __nv_bfloat16*>(aptr) + ((int64_t)slot * p.r_max + i_qr) * in_dim + k0;
+        if (nkp == 1) {
+          // the 8 rows are contiguous in the slab: one copy (each copy costs the TMA unit ~100 cycles)
+          if (lane == 0) {
+            mbar_arrive_expect_tx(fb, 8u * row_bytes);
+            bulk_g2s(sbase, src, 8u * row_bytes, fb);
           }
+        } else {
+          if (lane == 0) mbar_arrive_expect_tx(fb, 8u * row_bytes);
+          __syncwarp();
+          if (lane < 8) bulk_g2s(sbase + (uint32_t)(lane * pitchA), src + (int64_t)lane * in_dim, row_bytes, fb);
+        }
+        // advance: 8-row tiles inner, K parts outer
+        ++i_j;
+        i_qr += 8;
+        if (i_qr >= r_eff) { i_qr = 0; ++i_qs; }
+        if (i_j == nt_c) {
+          i_j = 0; i_qs = q0_s; i_qr = q0_r;
+          if (++i_kp == nkp) { i_kp = 0; i_shrink = 0; i_s = 0; i_et = 0; }
+        }
+      } else {
+#pragma unroll
+        for (int s = 0; s < B200_LORA_MAX_SLICES - 1; ++s)  // skip slices this CTA has no tiles of
+          if (i_s == s && i_et >= e_tiles[s]) { i_s = s + 1; i_et = 0; }
+        int lo = 0, en = 0, out = 0, left = 0;
+        const void* bptr = nullptr;
+#pragma unroll
+        for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) {
+          if (s == i_s) { lo = e_lo[s]; en = e_n[s]; out = p.st.out[s]; bptr = p.st.b[s]; left = e_tiles[s]; }
+          if (s > i_s) left += e_tiles[s];
+        }
+        const int r0 = i_et << p.er_shift;
+        const int nrows = min(ER, en - r0);
+        if (lane == 0) {
+          const uint32_t bytes = (uint32_t)nrows * (uint32_t)p.r_max * 2u;
+          mbar_arrive_expect_tx(fb, bytes);
+          const __nv_bfloat16* src =
+              static_cast<const __nv_bfloat16*>(bptr) + ((int64_t)slot * out + lo + r0) * p.r_max;
+          bulk_g2s(sbase, src, bytes, fb);
+        }
+        ++i_et;
+        // `left` = tiles of this and later slices; after the last one the next pass starts
+        // with its shrink tiles again
+        if (i_et >= left) {
+          i_shrink = shrink_tiles > 0 ? 1 : 0;
+          i_kp = 0; i_j = 0; i_qs = q0_s; i_qr = q0_r; i_s = 0; i_et = 0;
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(empty_bar(stage));
+      if (++p_stage == NS) { p_stage = 0; ++p_round; }
+      if (it + 1 == npro) {
+        B200_TRACE_PRODUCER(3)
+      }
     }
+    cluster_wait();
+    return;
+  }
 
-    // ===== cross-warp reduction of the K slices, scale, bf16, all-gather =====
+  // ============================= consumer warps =============================
+  // Token rows of the first pass (index metadata: safe before the wait). While the previous
+  // kernel finishes, pull this CTA's activation rows and its first output columns into L2:
+  // a prefetch never creates stale data (L2 is the point of coherence), it only hides the
+  // HBM latency of rows nobody has touched recently.
+  int tok0_lo = -1, tok0_hi = -1;
+  if (g < cnt) tok0_lo = p.sorted_idx[start + g];
+  if (g + 8 < cnt) tok0_hi = p.sorted_idx[start + g + 8];
+  if (tok0_lo >= p.T) tok0_lo = -1;
+  if (tok0_hi >= p.T) tok0_hi = -1;
+  if (p.use_pdl) {
     if (rows_c > 0) {
+      for (int kc = warp * 32 + t * 8; kc < in_dim; kc += kBgmvWarps * 32) {
+        if (tok0_lo >= 0) prefetch_l2(p.x + (int64_t)tok0_lo * p.x_ld + kc);
+        if (tok0_hi >= 0) prefetch_l2(p.x + (int64_t)tok0_hi * p.x_ld + kc);
+      }
+    }
 #pragma unroll
-      for (int j = 0; j < kBgmvMaxRc / 8; ++j) {
-        if (j < nt_c) {
-          float* r0 = red + ((size_t)warp * kBgmvTok + g) * p.red_pitch + 8 * j + 2 * t;
-          float* r1 = red + ((size_t)warp * kBgmvTok + g + 8) * p.red_pitch + 8 * j + 2 * t;
-          *reinterpret_cast<float2*>(r0) = make_float2(acc[j][0], acc[j][1]);
-          *reinterpret_cast<float2*>(r1) = make_float2(acc[j][2], acc[j][3]);
+    for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) {
+      if (s < n) {
+        for (int r = warp * 32 + t * 8; r < e_n[s]; r += kBgmvWarps * 32) {
+          const int cc = p.st.col[s] + e_lo[s] + r;
+          if (tok0_lo >= 0) prefetch_l2(p.y + (int64_t)tok0_lo * p.y_ld + cc);
+          if (tok0_hi >= 0) prefetch_l2(p.y + (int64_t)tok0_hi * p.y_ld + cc);
         }
       }
     }
-    __syncthreads();
-    cluster_wait();  // pairs with the arrive at kernel start / end of the previous pass
+    griddep_wait();  // x and y of this launch are final from here on
+  }
+  B200_TRACE_POINT(4)
+
+  int c_stage = 0, c_round = 0;  // stage / round of the tile being consumed
+  auto advance = [&]() {
+    if (++c_stage == NS) { c_stage = 0; ++c_round; }
+  };
+  const uint32_t pitchB = (uint32_t)p.r_max * 2u;
+  const int kblocks = r_eff >> 5;
+
+  for (int pass = 0; pass < npass; ++pass) {
+    const bool valid_lo = pass * kBgmvTok + g < cnt;
+    const bool valid_hi = pass * kBgmvTok + g + 8 < cnt;
+    int tok_lo = tok0_lo, tok_hi = tok0_hi;
+    if (pass > 0) {
+      tok_lo = tok_hi = -1;
+      if (valid_lo) tok_lo = p.sorted_idx[start + pass * kBgmvTok + g];
+      if (valid_hi) tok_hi = p.sorted_idx[start + pass * kBgmvTok + g + 8];
+      if (tok_lo >= p.T) tok_lo = -1;
+      if (tok_hi >= p.T) tok_hi = -1;
+    }
+
+    // y of this CTA's expand tiles is requested two tiles ahead (the first two right here, before
+    // the shrink), so the read-modify-write of y never waits for an L2 round trip.
+    int ys = 0, yet = 0, yleft = tiles_exp;  // cursor of the next tile whose y gets requested
+    auto y_next = [&](uint4& lo4, uint4& hi4, int& col_, int& nrows_, int& s_) {
+      lo4 = hi4 = make_uint4(0, 0, 0, 0);
+      col_ = 0; nrows_ = 0; s_ = 0;
+      if (yleft <= 0) return;
+      --yleft;
+#pragma unroll
+      for (int s = 0; s < B200_LORA_MAX_SLICES - 1; ++s)  // skip slices this CTA has no tiles of
+        if (ys == s && yet >= e_tiles[s]) { ys = s + 1; yet = 0; }
+      int lo = 0, en = 0, cb = 0;
+#pragma unroll
+      for (int s = 0; s < B200_LORA_MAX_SLICES; ++s)
+        if (s == ys) { lo = e_lo[s]; en = e_n[s]; cb = p.st.col[s]; }
+      const int r0 = yet << p.er_shift;
+      nrows_ = min(ER, en - r0);
+      col_ = cb + lo + r0;
+      s_ = ys;
+      ++yet;
+      if (warp * 32 + 8 * t < nrows_) {
+        const int cc = col_ + warp * 32 + 8 * t;
+        if (tok_lo >= 0) lo4 = ldg128(p.y + (int64_t)tok_lo * p.y_ld + cc);
+        if (tok_hi >= 0) hi4 = ldg128(p.y + (int64_t)tok_hi * p.y_ld + cc);
+      }
+    };
+    uint4 q0lo, q0hi, q1lo, q1hi;
+    int q0col, q0rows, q0s, q1col, q1rows, q1s;
+    y_next(q0lo, q0hi, q0col, q0rows, q0s);
+#if BGMV_YDEPTH == 2
+    y_next(q1lo, q1hi, q1col, q1rows, q1s);
+#else
+    q1lo = q1hi = make_uint4(0, 0, 0, 0); q1col = q1rows = q1s = 0;
+#endif
+
+    // ===== shrink: red[warp][tok][row] = x[16 tok, K blocks of this warp] . A_rows^T =====
+    for (int kp = 0; kp < (rows_c > 0 ? nkp : 0); ++kp) {
+      const int k0 = kp * KP;
+      // activation fragments of this warp's 32-column blocks, kept for all row tiles
+      uint4 xlo[kBgmvXBlocks], xhi[kBgmvXBlocks];
+#pragma unroll
+      for (int i = 0; i < kBgmvXBlocks; ++i) {
+        const int kl = (warp + kBgmvWarps * i) * 32;
+        const int kcol = k0 + kl + t * 8;
+        xlo[i] = xhi[i] = make_uint4(0, 0, 0, 0);
+        if (kl < KP && kcol < in_dim) {
+          if (tok_lo >= 0) xlo[i] = ldg128_nc(p.x + (int64_t)tok_lo * p.x_ld + kcol);
+          if (tok_hi >= 0) xhi[i] = ldg128_nc(p.x + (int64_t)tok_hi * p.x_ld + kcol);
+        }
+      }
+      for (int j = 0; j < nt_c; ++j) {
+        mbar_wait_bounded(full_bar(c_stage), (uint32_t)(c_round & 1), abort_flag);
+        if (kp == 0 && j == 0 && pass == 0) { B200_TRACE_POINT(5) }
+        const uint32_t sbase = ring_base + (uint32_t)c_stage * (uint32_t)p.stage_bytes;
+        // two independent accumulator chains halve the dependent-MMA latency
+        float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+        uint4 w[kBgmvXBlocks];
+#pragma unroll
+        for (int i = 0; i < kBgmvXBlocks; ++i) {
+          const int kl = (warp + kBgmvWarps * i) * 32;
+          w[i] = make_uint4(0, 0, 0, 0);
+          if (kl < KP && k0 + kl < in_dim) w[i] = lds128(sbase + (uint32_t)(g * pitchA) + (uint32_t)(kl + t * 8) * 2u);
+        }
+#pragma unroll
+        for (int i = 0; i < kBgmvXBlocks; ++i) {
+          mma_bf16_16816(acc, xlo[i].x, xhi[i].x, xlo[i].y, xhi[i].y, w[i].x, w[i].y);
+          mma_bf16_16816(acc2, xlo[i].z, xhi[i].z, xlo[i].w, xhi[i].w, w[i].z, w[i].w);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] += acc2[i];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(c_stage));
+        advance();
+        // acc holds (tok g | g+8, rank rows 8j+2t, 8j+2t+1): accumulate over K parts per warp
+        float2* r0 = reinterpret_cast<float2*>(red + ((size_t)warp * kBgmvTok + g) * p.red_pitch + 8 * j + 2 * t);
+        float2* r1 = reinterpret_cast<float2*>(red + ((size_t)warp * kBgmvTok + g + 8) * p.red_pitch + 8 * j + 2 * t);
+        if (kp == 0) {
+          *r0 = make_float2(acc[0], acc[1]);
+          *r1 = make_float2(acc[2], acc[3]);
+        } else {
+          const float2 a = *r0, b = *r1;
+          *r0 = make_float2(a.x + acc[0], a.y + acc[1]);
+          *r1 = make_float2(b.x + acc[2], b.y + acc[3]);
+        }
+      }
+    }
+    if (pass == 0) { B200_TRACE_POINT(6) }
+
+    // ===== cross-warp reduction of the K slices, scale, bf16, all-gather =====
+    named_bar_sync(1, kBgmvConsumers);
+    if (pass == 0) {
+      B200_TRACE_POINT(7)
+      cluster_wait();  // start-up barrier: peers run and their barriers are initialised
+    }
+    uint8_t* tmp_full = tmp_base + (size_t)(pass & 1) * p.tmp_bytes;
+    const uint32_t tmp_ready_bar = tmp_ready_bars + 8u * (uint32_t)(pass & 1);
     {
       const int half = rows_c >> 1;
-      for (int idx = tid; idx < kBgmvTok * half; idx += kBgmvThreads) {
-        const int tok = idx / half, pr = idx - tok * half;
+      const int tok = tid >> 4;
+      for (int pr = tid & 15; pr < half; pr += 16) {
         float s0 = 0.f, s1 = 0.f;
 #pragma unroll
         for (int w = 0; w < kBgmvWarps; ++w) {
@@ -286,99 +420,102 @@ __global__ void __launch_bounds__(kBgmvThreads, 1) bgmv_fused_kernel(const __gri
         for (int rc = 0; rc < C; ++rc) st_cluster_u32(mapa_shared(laddr, (uint32_t)rc), v);
       }
     }
-    cluster_arrive();
-    cluster_wait();
+    named_bar_sync(1, kBgmvConsumers);  // every store of this CTA is issued
+    if (tid < C) mbar_arrive_remote_release(mapa_shared(tmp_ready_bar, (uint32_t)tid));
+    if (pass == 0) { B200_TRACE_POINT(8) }
 
     // ===== expand: y[tok, cols] += tmp[16 tok, r] . B_rows^T ======================
-    int tok_lo = -1, tok_hi = -1;
-    if (valid_lo) tok_lo = p.sorted_idx[start + pass * kBgmvTok + g];
-    if (valid_hi) tok_hi = p.sorted_idx[start + pass * kBgmvTok + g + 8];
-    if (tok_lo >= p.T) tok_lo = -1;
-    if (tok_hi >= p.T) tok_hi = -1;
+    mbar_wait_bounded_acquire_cluster(tmp_ready_bar, (uint32_t)((pass >> 1) & 1), abort_flag);
+    if (pass == 0) { B200_TRACE_POINT(9) }
     const uint32_t tmp_lo = smem_u32(tmp_full + (size_t)g * p.pitchT);
     const uint32_t tmp_hi = smem_u32(tmp_full + (size_t)(g + 8) * p.pitchT);
-    const uint32_t pitchB = (uint32_t)p.r_max * 2u;
-    const int kblocks = r_eff >> 5;
 
+    for (int e = 0; e < tiles_exp; ++e) {
+      // y of tile e was requested two tiles ago; request tile e+2 now
+      const uint4 ylo = q0lo, yhi = q0hi;
+      const int col = q0col, nrows = q0rows, s_cur = q0s;
+#if BGMV_YDEPTH == 2
+      q0lo = q1lo; q0hi = q1hi; q0col = q1col; q0rows = q1rows; q0s = q1s;
+      y_next(q1lo, q1hi, q1col, q1rows, q1s);
+#else
+      y_next(q0lo, q0hi, q0col, q0rows, q0s);
+#endif
+      mbar_wait_bounded(full_bar(c_stage), (uint32_t)(c_round & 1), abort_flag);
+      if (pass == 0 && e < 5) { B200_TRACE_POINT(12 + 4 * e) }
+      const uint32_t sbase = ring_base + (uint32_t)c_stage * (uint32_t)p.stage_bytes;
+      const int rb = warp * 32;  // ER <= 256: one 32-row block per warp and tile
+      if (rb < nrows) {
+        float d[4][4];
 #pragma unroll
-    for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) {
-      if (s >= n) continue;
-      for (int et = 0; et < e_tiles[s]; ++et, ++it) {
-        const int stage = it % NS;
-        if (warp == 0 && it >= 1 && it - 1 + NS < total) {
-          const int prev = it - 1;
-          mbar_wait_bounded(empty_bar(prev % NS), (uint32_t)((prev / NS) & 1), abort_flag);
-          issue_tile(prev + NS, 3);
-        }
-        mbar_wait_bounded(full_bar(stage), (uint32_t)((it / NS) & 1), abort_flag);
-        const uint32_t sbase = smem_u32(ring + (size_t)stage * p.stage_bytes);
-        const int r0 = et * ER;
-        const int nrows = min(ER, e_n[s] - r0);
-        const int nblocks = ceil_div_i(nrows, 32);
-        const int col0 = p.st.col[s] + e_lo[s] + r0;
-        for (int blk = warp; blk < nblocks; blk += kBgmvWarps) {
-          float d[4][4];
+        for (int j = 0; j < 4; ++j) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.f;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          const uint32_t koff = (uint32_t)(s_cur * r_eff + kb * 32 + t * 8) * 2u;
+          const uint4 alo = lds128(tmp_lo + koff);
+          const uint4 ahi = lds128(tmp_hi + koff);
+          const uint32_t woff = (uint32_t)(kb * 32 + t * 8) * 2u;
+          uint4 w[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.f;
-          const int rb = blk * 32;
-          for (int kb = 0; kb < kblocks; ++kb) {
-            const uint32_t koff = (uint32_t)(s * r_eff + kb * 32 + t * 8) * 2u;
-            const uint4 alo = lds128(tmp_lo + koff);
-            const uint4 ahi = lds128(tmp_hi + koff);
-            const uint32_t woff = (uint32_t)(kb * 32 + t * 8) * 2u;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              // MMA column n of tile j reads slab row 8*(n/2) + 2j + (n%2): thread (g,t)
-              // then owns 8 consecutive output columns 8t..8t+7 of the block.
-              const int prow = rb + 8 * (g >> 1) + 2 * j + (g & 1);
-              const uint4 w = lds128(sbase + (uint32_t)prow * pitchB + woff);
-              mma_bf16_16816(d[j], alo.x, ahi.x, alo.y, ahi.y, w.x, w.y);
-              mma_bf16_16816(d[j], alo.z, ahi.z, alo.w, ahi.w, w.z, w.w);
-            }
+          for (int j = 0; j < 4; ++j) {
+            // MMA column n of tile j reads slab row 8*(n/2) + 2j + (n%2): thread (g,t)
+            // then owns 8 consecutive output columns 8t..8t+7 of the block.
+            const int prow = rb + 8 * (g >> 1) + 2 * j + (g & 1);
+            w[j] = lds128(sbase + (uint32_t)prow * pitchB + woff);
           }
-          if (rb + 8 * t < nrows) {
-            const int col = col0 + rb + 8 * t;
-            if (tok_lo >= 0) {
-              uint4* yp = reinterpret_cast<uint4*>(p.y + (int64_t)tok_lo * p.y_ld + col);
-              uint4 v = *yp;
-              v.x = pack_bf16x2(bf16_lo(v.x) + d[0][0], bf16_hi(v.x) + d[0][1]);
-              v.y = pack_bf16x2(bf16_lo(v.y) + d[1][0], bf16_hi(v.y) + d[1][1]);
-              v.z = pack_bf16x2(bf16_lo(v.z) + d[2][0], bf16_hi(v.z) + d[2][1]);
-              v.w = pack_bf16x2(bf16_lo(v.w) + d[3][0], bf16_hi(v.w) + d[3][1]);
-              *yp = v;
-            }
-            if (tok_hi >= 0) {
-              uint4* yp = reinterpret_cast<uint4*>(p.y + (int64_t)tok_hi * p.y_ld + col);
-              uint4 v = *yp;
-              v.x = pack_bf16x2(bf16_lo(v.x) + d[0][2], bf16_hi(v.x) + d[0][3]);
-              v.y = pack_bf16x2(bf16_lo(v.y) + d[1][2], bf16_hi(v.y) + d[1][3]);
-              v.z = pack_bf16x2(bf16_lo(v.z) + d[2][2], bf16_hi(v.z) + d[2][3]);
-              v.w = pack_bf16x2(bf16_lo(v.w) + d[3][2], bf16_hi(v.w) + d[3][3]);
-              *yp = v;
-            }
-          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) mma_bf16_16816(d[j], alo.x, ahi.x, alo.y, ahi.y, w[j].x, w[j].y);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) mma_bf16_16816(d[j], alo.z, ahi.z, alo.w, ahi.w, w[j].z, w[j].w);
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar(stage));
+        if (lane == 0) mbar_arrive(empty_bar(c_stage));  // the stage is in registers now
+        if (pass == 0 && e < 5) { B200_TRACE_POINT(13 + 4 * e) }
+        if (rb + 8 * t < nrows) {
+          const int cc = col + rb + 8 * t;
+          if (tok_lo >= 0) {
+            uint4 v = ylo;
+            v.x = add_bf16x2(v.x, d[0][0], d[0][1]);
+            v.y = add_bf16x2(v.y, d[1][0], d[1][1]);
+            v.z = add_bf16x2(v.z, d[2][0], d[2][1]);
+            v.w = add_bf16x2(v.w, d[3][0], d[3][1]);
+            stg128(p.y + (int64_t)tok_lo * p.y_ld + cc, v);
+          }
+          if (tok_hi >= 0) {
+            uint4 v = yhi;
+            v.x = add_bf16x2(v.x, d[0][2], d[0][3]);
+            v.y = add_bf16x2(v.y, d[1][2], d[1][3]);
+            v.z = add_bf16x2(v.z, d[2][2], d[2][3]);
+            v.w = add_bf16x2(v.w, d[3][2], d[3][3]);
+            stg128(p.y + (int64_t)tok_hi * p.y_ld + cc, v);
+          }
+        }
+      } else {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(c_stage));
       }
+      if (pass == 0 && e < 5) { B200_TRACE_POINT(14 + 4 * e) }
+      advance();
     }
-    // tmp of this pass is no longer needed: peers may overwrite it in the next pass
-    if (pass + 1 < npass) cluster_arrive();
+    if (pass == 0) { B200_TRACE_POINT(10) }
   }
+  B200_TRACE_POINT(11)
   if (tid == 0 && *abort_flag != 0) atomicOr(&g_b200_status, kStatusWaitGaveUp);
 }
 
 // ------------------------------------------------------------------ host side
 struct BgmvOptions {
-  int cluster = 0;  // 0 = auto
+  int cluster = 0;   // 0 = auto
   int pdl = 1;
+  int ring_kb = 0;   // cap of the stage ring in KB (0 = default)
 };
 inline BgmvOptions& bgmv_options() {
   static BgmvOptions o;
   return o;
 }
+constexpr int kBgmvDefaultRingKb = 200;  // as many tiles in flight as fit (measured best on B200)
 
 inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
+inline int floor_pow2(int v) { int r = 1; while (r * 2 <= v) r *= 2; return r; }
+inline int log2_exact(int v) { int s = 0; while ((1 << s) < v) ++s; return s; }
 
 // Fills `pp` with the tiling for this problem; returns false (and a reason) when
 // the fused kernel cannot run it.
@@ -420,30 +557,36 @@ inline bool bgmv_plan(const BgmvProblem& b, BgmvParams* pp, const char** why) {
   p.rank_per_slot = b.rank_per_slot; p.scale_per_slot = b.scale_per_slot;
   p.sorted_idx = b.sorted_idx; p.slot_ids = b.slot_ids; p.counts = b.counts; p.offsets = b.offsets;
   p.n_buckets = b.n_buckets; p.scaling = b.scaling;
-  p.C = C;
-  const int rows_stage = Rc + kBgmvTok;
-  p.KC = (b.in_dim >= 512 && rows_stage * (512 * 2 + 64) <= kBgmvStageMax) ? 512 : 256;
-  p.pitchA = p.KC * 2 + 64;
-  const int stageA = rows_stage * p.pitchA;
-  int oc_max = 0, tiles = ceil_div_i(b.in_dim, p.KC);
-  for (int s = 0; s < st.n; ++s) oc_max = std::max(oc_max, round_up_i(ceil_div_i(st.out[s], C), 32));
-  p.ER = std::min(oc_max, (kBgmvStageMax / (b.r_max * 2)) / 32 * 32);
-  for (int s = 0; s < st.n; ++s) tiles += ceil_div_i(round_up_i(ceil_div_i(st.out[s], C), 32), p.ER);
+  p.c_shift = log2_exact(C);
+  p.KP = std::min(b.in_dim, kBgmvKP);
+  p.nkp = ceil_div_i(b.in_dim, p.KP);
+  p.pitchA = p.KP * 2 + (p.nkp > 1 ? 64 : 0);  // dense when a tile is one contiguous copy
+  const int stageA = 8 * p.pitchA;
+  p.ER = std::max(32, std::min(256, floor_pow2(16384 / (b.r_max * 2))));
+  p.er_shift = log2_exact(p.ER);
+  int tiles = (Rc / 8) * p.nkp;
+  for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) p.oc[s] = 0;
+  for (int s = 0; s < st.n; ++s) {
+    p.oc[s] = round_up_i(ceil_div_i(st.out[s], C), 32);
+    tiles += ceil_div_i(p.oc[s], p.ER);
+  }
   const int stageB = p.ER * b.r_max * 2;
-  p.stage_bytes = round_up_i(std::max(stageA, stageB), 1024);
+  p.stage_bytes = round_up_i(std::max(stageA, stageB), 128);
   p.red_pitch = Rc + 2;
   const int red_bytes = round_up_i(kBgmvWarps * kBgmvTok * p.red_pitch * 4, 128);
   p.pitchT = round_up_i(Q * 2, 128) + 64;
-  const int tmp_bytes = round_up_i(kBgmvTok * p.pitchT, 128);
+  p.tmp_bytes = round_up_i(kBgmvTok * p.pitchT, 128);
   const int bar_bytes = 256;
-  const int fixed = red_bytes + tmp_bytes + bar_bytes;
+  const int fixed = red_bytes + 2 * p.tmp_bytes + bar_bytes;
+  const int ring_kb = bgmv_options().ring_kb > 0 ? bgmv_options().ring_kb : kBgmvDefaultRingKb;
   int NS = std::min(std::max(tiles, 2), (kBgmvSmemMax - fixed) / p.stage_bytes);
-  NS = std::min(NS, 12);
+  NS = std::min(NS, kBgmvMaxStages);
+  NS = std::min(NS, std::max(2, ring_kb * 1024 / p.stage_bytes));
   if (NS < 2) { *why = "shared memory too small for two stages"; return false; }
   p.NS = NS;
   p.off_red = NS * p.stage_bytes;
   p.off_tmp = p.off_red + red_bytes;
-  p.off_bar = p.off_tmp + tmp_bytes;
+  p.off_bar = p.off_tmp + 2 * p.tmp_bytes;
   p.use_pdl = bgmv_options().pdl ? 1 : 0;
   if (pp != nullptr) *pp = p;
   return true;
@@ -465,14 +608,14 @@ inline int bgmv_launch(const BgmvProblem& b, cudaStream_t stream) {
     configured_device = dev;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)p.C, (unsigned)p.n_buckets, 1);
+  cfg.gridDim = dim3(1u << p.c_shift, (unsigned)p.n_buckets, 1);
   cfg.blockDim = dim3(kBgmvThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
   int na = 0;
   attrs[na].id = cudaLaunchAttributeClusterDimension;
-  attrs[na].val.clusterDim.x = (unsigned)p.C;
+  attrs[na].val.clusterDim.x = 1u << p.c_shift;
   attrs[na].val.clusterDim.y = 1;
   attrs[na].val.clusterDim.z = 1;
   ++na;

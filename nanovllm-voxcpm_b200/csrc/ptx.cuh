@@ -31,14 +31,30 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrive on an mbarrier of another CTA of the cluster (address from mapa_shared); the
+// release at cluster scope publishes this CTA's earlier distributed-shared-memory stores.
+__device__ __forceinline__ void mbar_arrive_remote_release(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(2000u)  // suspend-time hint, ns
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_wait_acquire_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }
@@ -47,10 +63,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // *abort_flag (shared memory); once it is raised every later wait of the CTA
 // returns at once, so control flow never depends on a barrier that cannot
 // complete. Returns false when it gave up.
-constexpr int kSpinLimit = 1 << 20;
+constexpr int kSpinLimit = 1 << 22;
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   for (int it = 0; it < kSpinLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ bool mbar_wait_bounded_acquire_cluster(uint32_t bar, uint32_t parity,
+                                                                  volatile int* abort_flag) {
+  for (int it = 0; it < kSpinLimit; ++it) {
+    if (mbar_try_wait_acquire_cluster(bar, parity)) return true;
     if (*abort_flag != 0) return false;
   }
   *abort_flag = 1;
@@ -73,11 +98,6 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
 }
-__device__ __forceinline__ uint32_t cluster_nctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
-  return r;
-}
 __device__ __forceinline__ uint32_t mapa_shared(uint32_t local_addr, uint32_t cta_rank) {
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(cta_rank));
@@ -93,17 +113,39 @@ __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
 
+// barrier among a subset of the CTA's warps (id 1..15, thread count a multiple of 32)
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // ------------------------------------------ programmatic dependent launch
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-// ------------------------------------------------------------ shared loads
+// ------------------------------------------------------------ loads / stores
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
+}
+// 16-byte global load through the read-only path (data not written by this kernel)
+__device__ __forceinline__ uint4 ldg128_nc(const void* gptr) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(gptr));
+  return v;
+}
+__device__ __forceinline__ void prefetch_l2(const void* gptr) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(gptr));
+}
+__device__ __forceinline__ uint4 ldg128(const void* gptr) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(gptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void stg128(void* gptr, uint4 v) {
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(gptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
 // ------------------------------------------------- warp MMA, bf16 -> fp32
@@ -123,5 +165,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+// two packed bf16 + two fp32 deltas, rounded once
+__device__ __forceinline__ uint32_t add_bf16x2(uint32_t y, float d0, float d1) {
+  return pack_bf16x2(bf16_lo(y) + d0, bf16_hi(y) + d1);
+}
 
 }  // namespace b200lora
