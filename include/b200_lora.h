@@ -89,8 +89,9 @@ const char* lora_b200_last_error(void);
  *                  conventions: eager plan, graph buffers with a leading -1 bucket,
  *                  vLLM-style with a counted -1 bucket). With the bucket arrays NULL
  *                  only the generic kernel can run.
- *  workspace       device scratch for B200_LORA_IMPL_SGMV (see
- *                  lora_b200_workspace_bytes), otherwise may be NULL.
+ *  workspace       device scratch for B200_LORA_IMPL_SGMV (see lora_b200_workspace_bytes); may be
+ *                  NULL otherwise. With B200_LORA_IMPL_AUTO the prefill kernels are chosen only
+ *                  when enough scratch is passed.
  */
 int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
                   int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
@@ -100,6 +101,11 @@ int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T,
                   const int32_t* counts, const int32_t* offsets, int32_t n_buckets, float scaling,
                   int32_t dtype, int32_t impl, void* workspace, size_t workspace_bytes,
                   void* stream);
+
+/* Bytes of device scratch that B200_LORA_IMPL_SGMV needs for a batch of T tokens (the
+ * [n_slices, T, r_max] shrink result in bf16, plus alignment slack). The reference allocates this
+ * intermediate itself on every call (nanovllm_voxcpm/lora.py:302). */
+size_t lora_b200_workspace_bytes(int32_t T, int32_t n_slices, int32_t r_max);
 
 /*
  * out[s, t, 0:r_max] = scaling * x[t] . A_s[slot_t]^T for slot_t >= 0, and 0 for

@@ -48,6 +48,7 @@ _SIGNATURES = {
         [c_void_p, c_int64, c_void_p, c_int32, c_int32, c_int32, POINTER(c_void_p), POINTER(c_int32),
          POINTER(c_int32), c_int32, c_int32, c_void_p, c_int32, c_int32, c_void_p],
     ),
+    "lora_b200_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
     "lora_b200_set_option": (c_int32, [c_int32, c_int32]),
     "lora_b200_device_status": (c_int32, [POINTER(c_int32), c_int32]),
 }
@@ -144,3 +145,7 @@ def device_status(reset: bool = False) -> int:
     out = c_int32(0)
     check(lib().lora_b200_device_status(ctypes.byref(out), 1 if reset else 0))
     return out.value
+
+
+def workspace_bytes(T: int, n_slices: int, r_max: int) -> int:
+    return int(lib().lora_b200_workspace_bytes(T, n_slices, r_max))

@@ -3,6 +3,7 @@
 #include "common.cuh"
 #include "generic.cuh"
 #include "bgmv_fused.cuh"
+#include "sgmv_tc.cuh"
 
 using namespace b200lora;
 
@@ -119,6 +120,11 @@ int lora_b200_device_status(int32_t* status, int32_t reset) {
   return B200_LORA_OK;
 }
 
+size_t lora_b200_workspace_bytes(int32_t T, int32_t n_slices, int32_t r_max) {
+  if (T < 0 || n_slices < 1 || r_max < 1) return 0;
+  return sgmv_workspace_bytes(T, n_slices, r_max);
+}
+
 int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
                   int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
                   const int32_t* out_sizes, const int32_t* col_offsets, int32_t S, int32_t r_max,
@@ -127,8 +133,6 @@ int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T,
                   const int32_t* counts, const int32_t* offsets, int32_t n_buckets, float scaling,
                   int32_t dtype, int32_t impl, void* workspace, size_t workspace_bytes,
                   void* stream) {
-  (void)workspace;
-  (void)workspace_bytes;
   if (!valid_dtype(dtype)) return fail(B200_LORA_EINVAL, "unknown dtype %d", dtype);
   if (T < 0 || in_dim < 1 || S < 1 || r_max < 1)
     return fail(B200_LORA_EINVAL, "bad sizes T=%d in=%d S=%d r_max=%d", T, in_dim, S, r_max);
@@ -158,9 +162,22 @@ int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T,
   bp.sorted_idx = sorted_idx; bp.slot_ids = slot_ids; bp.counts = counts; bp.offsets = offsets;
   bp.n_buckets = n_buckets; bp.scaling = scaling;
 
+  SgmvProblem sp;
+  sp.y = y; sp.y_ld = y_ld; sp.x = x; sp.x_ld = x_ld; sp.T = T; sp.in_dim = in_dim; sp.S = S; sp.r_max = r_max;
+  sp.st = st; sp.scale_per_slot = scale_per_slot; sp.token_to_slot = token_to_slot; sp.scaling = scaling;
+
   if (impl == B200_LORA_IMPL_AUTO) {
-    impl = (dtype == B200_LORA_BF16 && have_buckets && bgmv_supported(bp, nullptr)) ? B200_LORA_IMPL_BGMV
-                                                                                    : B200_LORA_IMPL_GENERIC;
+    // Long batches (prefill) go to the tensor-core kernels when scratch memory was supplied, decode
+    // batches to the fused kernel, everything else (other dtypes, odd shapes) to the generic one.
+    int n_act = 0;
+    for (int s = 0; s < st.n; ++s) n_act += st.out[s] > 0;
+    if (dtype == B200_LORA_BF16 && T >= kSgmvAutoMinTokens && sgmv_supported(sp, nullptr) && workspace != nullptr &&
+        workspace_bytes >= sgmv_workspace_bytes(T, n_act, r_max))
+      impl = B200_LORA_IMPL_SGMV;
+    else if (dtype == B200_LORA_BF16 && have_buckets && bgmv_supported(bp, nullptr))
+      impl = B200_LORA_IMPL_BGMV;
+    else
+      impl = B200_LORA_IMPL_GENERIC;
   }
   switch (impl) {
     case B200_LORA_IMPL_GENERIC:
@@ -180,6 +197,9 @@ int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T,
       if (!bgmv_supported(bp, &why)) return fail(B200_LORA_EUNSUPPORTED, "fused decode kernel: %s", why);
       return bgmv_launch(bp, st_);
     }
+    case B200_LORA_IMPL_SGMV:
+      if (dtype != B200_LORA_BF16) return fail(B200_LORA_EUNSUPPORTED, "prefill kernels are bf16 only");
+      return sgmv_launch(sp, workspace, workspace_bytes, st_);
     default:
       return fail(B200_LORA_EUNSUPPORTED, "impl %d is not available", impl);
   }

@@ -99,6 +99,24 @@ def _i32(t: torch.Tensor | None, name: str) -> torch.Tensor | None:
     return t
 
 
+#: batches of at least this many rows use the tensor-core prefill kernels under IMPL_AUTO
+SGMV_MIN_TOKENS = 512
+
+_SCRATCH: dict[torch.device, torch.Tensor] = {}
+
+
+def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Grow-only per-device scratch buffer for the prefill kernels' rank-r intermediate.
+
+    The reference allocates this intermediate on every call (``lora.py:302``); here one buffer
+    per device is reused, so steady-state calls (and CUDA-graph replays) allocate nothing."""
+    buf = _SCRATCH.get(device)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _SCRATCH[device] = buf
+    return buf
+
+
 def launch_add(
     y_packed: torch.Tensor,
     x: torch.Tensor,
@@ -146,6 +164,10 @@ def launch_add(
     if n_buckets <= 0:
         srt = ids = cnt = off = None
         n_buckets = 0
+    if workspace is None and x.dtype == torch.bfloat16 and (
+        impl == N.IMPL_SGMV or (impl == N.IMPL_AUTO and T >= SGMV_MIN_TOKENS)
+    ):
+        workspace = scratch_for(x.device, N.workspace_bytes(T, len(a_slabs), r_max))
     with torch.cuda.device(x.device):
         rc = N.lib().lora_b200_add(
             y_packed.data_ptr(), y_packed.stride(0), x.data_ptr(), x.stride(0), T, in_dim, len(a_slabs),

@@ -355,3 +355,66 @@ def test_cuda_graph_replay_with_changing_slots_and_weights():
         base = (x.float().cpu() @ layer.weight.data.float().cpu().T).to(torch.bfloat16)
         ref = O.add_lora(base, x.cpu(), a_slabs, b_slabs, slots, 1.0, [0, 1024, 1152])
         assert_lora_close(out, ref, max_abs=4e-2, what=f"graph step {step}")  # base GEMM rounding included
+
+
+# ------------------------------------------------------------------ prefill SGMV (tcgen05)
+@pytest.mark.parametrize("name", ["qkv", "o", "gate_up", "down"])
+def test_prefill_projection_matches_oracle(name):
+    """Prefill config at reduced length (5 requests, 602 rows, mixed ranks 8/16/64 in a rank-64 slab):
+    tensor-core kernels vs oracle; rows of a request boundary share a 128-row block."""
+    p = W.prefill_projection(name, seed=3, lengths=[200, 77, 133, 128, 64])
+    p.token_to_slot[10:25] = -1  # a hole without adapter inside the first request
+    out, y_in = run_add(p, N.IMPL_SGMV)
+    check_against_oracle(p, out, y_in, what=f"sgmv/{name}")
+    out2, _ = run_add(p, N.IMPL_SGMV)
+    assert torch.equal(out.view(torch.int16), out2.view(torch.int16)), "two runs differ bitwise"
+    auto, _ = run_add(p, N.IMPL_AUTO)  # 602 rows >= 512: auto picks the prefill kernels
+    assert torch.equal(out.view(torch.int16), auto.view(torch.int16))
+
+
+@pytest.mark.parametrize("r_max", [16, 32, 64])
+def test_sgmv_ranks_scales_strides_and_ragged_length(r_max):
+    lengths = [130, 1, 255, 7, 64]  # T = 457: not a multiple of 128, runs of length 1 and 7
+    slots = []
+    for i, n in enumerate(lengths):
+        slots += [i % 3] * n
+    p = W.make_projection(17 + r_max, len(slots), 512, [384, 0, 128], 3, r_max, token_to_slot=slots)
+    p.a_slabs[1] = p.a_slabs[0]
+    sps = torch.tensor([1.0, 0.5, 2.0])
+    out, y_in = run_add(p, N.IMPL_SGMV, scaling=0.5, scale_per_slot=sps, y_pad=16, x_pad=8)
+    check_against_oracle(p, out, y_in, 0.5, sps, what=f"sgmv r={r_max}")
+
+
+def test_sgmv_random_slots_and_full_size_properties():
+    # decode-like random map through the prefill kernels: many one-row runs per block (slow path, still exact)
+    p = W.make_projection(23, 200, 256, [256], 8, 32, p_none=0.2)
+    out, y_in = run_add(p, N.IMPL_SGMV)
+    check_against_oracle(p, out, y_in, what="sgmv random slots")
+    # full prefill size (8192 rows): linearity of the delta in x, checked without the oracle
+    big = W.prefill_projection("o", seed=0).to_device(DEV)
+    S = big.a_slabs[0].shape[0]
+    meta = metadata_for(big.token_to_slot, "eager", S)
+    zeros = torch.zeros_like(big.y)
+    y1, y2 = zeros.clone(), zeros.clone()
+    LORA.launch_add(y1, big.x, big.a_slabs, big.b_slabs, big.out_sizes, big.col_offsets, meta, 1.0, impl=N.IMPL_SGMV)
+    LORA.launch_add(y2, big.x * 2, big.a_slabs, big.b_slabs, big.out_sizes, big.col_offsets, meta, 1.0, impl=N.IMPL_SGMV)
+    torch.cuda.synchronize()
+    assert float(y1.float().abs().max()) > 0
+    torch.testing.assert_close(y2.float(), 2 * y1.float(), atol=2e-2, rtol=2e-2)
+    # and against the fused decode kernel on the same full-size input (independent implementation)
+    y3 = zeros.clone()
+    LORA.launch_add(y3, big.x, big.a_slabs, big.b_slabs, big.out_sizes, big.col_offsets, meta, 1.0, impl=N.IMPL_BGMV)
+    torch.cuda.synchronize()
+    assert_lora_close(y1, y3.float(), what="sgmv vs fused decode kernel at 8192 rows")
+
+
+def test_sgmv_unsupported_and_workspace_errors():
+    p = W.make_projection(4, 64, 96, [64], 2, 32)  # in % 64 != 0
+    with pytest.raises(RuntimeError, match="prefill kernels"):
+        run_add(p, N.IMPL_SGMV)
+    d = W.make_projection(4, 64, 128, [64], 2, 32).to_device(DEV)
+    meta = metadata_for(d.token_to_slot, "eager", 2)
+    tiny = torch.empty(16, dtype=torch.uint8, device=DEV)
+    with pytest.raises(RuntimeError, match="scratch"):
+        LORA.launch_add(d.y, d.x, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets, meta, 1.0, impl=N.IMPL_SGMV, workspace=tiny)
+    assert N.workspace_bytes(8192, 3, 64) >= 3 * 8192 * 64 * 2
