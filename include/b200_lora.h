@@ -135,6 +135,38 @@ int lora_b200_expand(void* y, int64_t y_ld, const void* tmp, int32_t tmp_dtype, 
                      const int32_t* token_to_slot, int32_t add_inputs, int32_t dtype,
                      void* stream);
 
+/*
+ * Prefill multi-LoRA add for callers that cannot allocate device memory (code running
+ * under CUDA-graph capture or replay, plug-ins that only receive input / output buffers
+ * from their host framework, latency-critical loops that must stay away from cudaMalloc).
+ * Same result as lora_b200_add with B200_LORA_IMPL_SGMV, but the rank-r intermediate lives
+ * in a fixed array inside the library instead of caller-provided scratch; no allocation of
+ * any kind happens in this call. It has no counterpart in the reference, whose backend
+ * allocates that intermediate with torch.empty on every call.
+ *
+ * Limits and rules:
+ *  - the batch must fit the built-in scratch: lora_b200_workspace_bytes(T, active slices,
+ *    r_max) <= lora_b200_static_scratch_bytes() (8 MiB); larger batches are rejected with
+ *    B200_LORA_EWORKSPACE and nothing is launched;
+ *  - bf16 only, shapes as for B200_LORA_IMPL_SGMV (r_max 16/32/64, in % 64 == 0);
+ *  - the first call on each GPU looks up the array's device address (cudaGetSymbolAddress,
+ *    which may load the module): make that first call outside of any stream capture;
+ *  - there is one array per GPU, shared by all calls and still holding the previous call's
+ *    intermediate; calls that may overlap on the GPU (different streams without ordering)
+ *    race on it. Calls on one stream are safe.
+ * Arguments have the meaning they have in lora_b200_add.
+ */
+int lora_b200_add_prefill_noalloc(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T,
+                                  int32_t in_dim, int32_t n_slices, const void* const* a_slabs,
+                                  const void* const* b_slabs, const int32_t* out_sizes,
+                                  const int32_t* col_offsets, int32_t S, int32_t r_max,
+                                  const float* scale_per_slot, const int32_t* token_to_slot,
+                                  float scaling, void* stream);
+
+/* Size in bytes of the built-in scratch used by lora_b200_add_prefill_noalloc. No counterpart in
+ * the reference. */
+size_t lora_b200_static_scratch_bytes(void);
+
 /* Tuning knobs of the fused decode kernel (process-wide, read at launch time). */
 #define B200_LORA_OPT_CLUSTER 1 /* CTAs per slot bucket: 1, 2, 4, 8; 0 = choose from n_buckets */
 #define B200_LORA_OPT_PDL 2     /* 1 = launch with programmatic stream serialization (default), 0 = off */

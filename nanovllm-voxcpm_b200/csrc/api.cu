@@ -258,3 +258,88 @@ int lora_b200_expand(void* y, int64_t y_ld, const void* tmp, int32_t tmp_dtype, 
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Prefill entry point for callers that cannot allocate device memory.
+//
+// The tensor-core prefill kernels keep the rank-r shrink result in scratch memory that
+// lora_b200_add expects from its caller. Some callers have nowhere to get that from: code
+// running inside an already captured or replaying CUDA graph, plug-ins that are handed
+// input / output buffers by a host framework and are forbidden to call the allocator, and
+// latency-critical loops that must not touch cudaMalloc (it synchronises the device). For them
+// the same two kernels run on a fixed scratch array that is part of the library image.
+//
+// The array is one per GPU (every device that loads this library carries these bytes until
+// the process exits) and is shared by every call on that GPU: it still holds the previous
+// call's intermediate, and two calls that overlap on the GPU (different streams) would
+// overwrite each other's intermediate. Nothing in it has to start at zero: each row that a
+// call reads and uses was written by that same call's shrink kernel, rows of tokens without
+// an adapter are read but masked out.
+namespace {
+
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB: e.g. 3 slices x 8192 tokens x rank 64 in bf16 = 3 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device. In host code the array's name is
+// only a handle of the runtime, not a device pointer, so the address is asked for once per
+// device (with that device current) and remembered.
+int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(B200_LORA_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(B200_LORA_EUNSUPPORTED, "device ordinal %d not supported", dev);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(B200_LORA_ECUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return B200_LORA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t lora_b200_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int lora_b200_add_prefill_noalloc(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
+                                  int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
+                                  const int32_t* out_sizes, const int32_t* col_offsets, int32_t S, int32_t r_max,
+                                  const float* scale_per_slot, const int32_t* token_to_slot, float scaling,
+                                  void* stream) {
+  if (T < 0 || in_dim < 1 || S < 1 || r_max < 1)
+    return fail(B200_LORA_EINVAL, "bad sizes T=%d in=%d S=%d r_max=%d", T, in_dim, S, r_max);
+  if (T == 0) return B200_LORA_OK;
+  if (y == nullptr || x == nullptr || token_to_slot == nullptr || out_sizes == nullptr || col_offsets == nullptr)
+    return fail(B200_LORA_EINVAL, "null pointer argument");
+  SliceTable st;
+  if (int rc = fill_slices(st, n_slices, a_slabs, b_slabs, out_sizes, col_offsets, true, true)) return rc;
+  int n_act = 0;
+  int64_t width = 0;
+  for (int s = 0; s < st.n; ++s) {
+    n_act += st.out[s] > 0;
+    width = width > (int64_t)st.col[s] + st.out[s] ? width : (int64_t)st.col[s] + st.out[s];
+  }
+  if (n_act == 0) return B200_LORA_OK;
+  if (y_ld < width || x_ld < in_dim) return fail(B200_LORA_EINVAL, "row stride smaller than row");
+  const size_t need = sgmv_workspace_bytes(T, n_act, r_max);
+  if (need > kStaticScratchBytes)
+    return fail(B200_LORA_EWORKSPACE,
+                "batch needs %zu bytes of scratch (slices %d x tokens %d x rank %d, bf16) but the built-in scratch "
+                "holds %zu; use lora_b200_add with caller-provided scratch",
+                need, n_act, T, r_max, kStaticScratchBytes);
+  SgmvProblem sp;
+  sp.y = y; sp.y_ld = y_ld; sp.x = x; sp.x_ld = x_ld; sp.T = T; sp.in_dim = in_dim; sp.S = S; sp.r_max = r_max;
+  sp.st = st; sp.scale_per_slot = scale_per_slot; sp.token_to_slot = token_to_slot; sp.scaling = scaling;
+  void* scratch = nullptr;
+  if (int rc = static_scratch_for_current_device(&scratch)) return rc;
+  return sgmv_launch(sp, scratch, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
