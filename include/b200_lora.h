@@ -102,6 +102,28 @@ int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T,
                   int32_t dtype, int32_t impl, void* workspace, size_t workspace_bytes,
                   void* stream);
 
+/*
+ * y = x . W^T (+ bias) + LoRA delta in one pass over y: the base GEMM runs on the tensor cores
+ * and, for every 128-row block whose rows use one adapter slot, the delta tmp . B^T is
+ * accumulated into the same TMEM accumulator before the single store of y (blocks with mixed
+ * slots get their delta from the run-based expand kernel afterwards).
+ *
+ * Replaces the `F.linear` + `add_lora` pair of the layer forwards
+ * (nanovllm_voxcpm/layers/lora.py:341-366, 547-570, 723-738, 832-848).
+ *  weight      device; [out_total, in] bf16, row pitch w_ld elements
+ *  bias        device bf16[out_total] or NULL
+ *  token_to_slot NULL or n_slices == 0: plain linear, no adapter work
+ *  workspace   device scratch of lora_b200_workspace_bytes(T, active slices, r_max) bytes
+ *              (may be NULL for a plain linear)
+ * bf16 only; in % 64 == 0; r_max in {16, 32, 64}. Other arguments as in lora_b200_add.
+ */
+int lora_b200_linear_lora(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
+                          const void* weight, int64_t w_ld, int32_t out_total, const void* bias,
+                          int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
+                          const int32_t* out_sizes, const int32_t* col_offsets, int32_t S,
+                          int32_t r_max, const float* scale_per_slot, const int32_t* token_to_slot,
+                          float scaling, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Bytes of device scratch that B200_LORA_IMPL_SGMV needs for a batch of T tokens (the
  * [n_slices, T, r_max] shrink result in bf16, plus alignment slack). The reference allocates this
  * intermediate itself on every call (nanovllm_voxcpm/lora.py:302). */

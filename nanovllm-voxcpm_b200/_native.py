@@ -49,6 +49,12 @@ _SIGNATURES = {
          POINTER(c_int32), c_int32, c_int32, c_void_p, c_int32, c_int32, c_void_p],
     ),
     "lora_b200_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
+    "lora_b200_linear_lora": (
+        c_int32,
+        [c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_void_p, c_int64, c_int32, c_void_p, c_int32,
+         POINTER(c_void_p), POINTER(c_void_p), POINTER(c_int32), POINTER(c_int32), c_int32, c_int32, c_void_p,
+         c_void_p, c_float, c_void_p, c_size_t, c_void_p],
+    ),
     "lora_b200_add_prefill_noalloc": (
         c_int32,
         [c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32, POINTER(c_void_p), POINTER(c_void_p),

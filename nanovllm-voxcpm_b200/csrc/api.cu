@@ -4,6 +4,7 @@
 #include "generic.cuh"
 #include "bgmv_fused.cuh"
 #include "sgmv_tc.cuh"
+#include "gemm_tc.cuh"
 
 using namespace b200lora;
 
@@ -120,6 +121,34 @@ int lora_b200_device_status(int32_t* status, int32_t reset) {
   return B200_LORA_OK;
 }
 
+int lora_b200_linear_lora(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
+                          const void* weight, int64_t w_ld, int32_t out_total, const void* bias, int32_t n_slices,
+                          const void* const* a_slabs, const void* const* b_slabs, const int32_t* out_sizes,
+                          const int32_t* col_offsets, int32_t S, int32_t r_max, const float* scale_per_slot,
+                          const int32_t* token_to_slot, float scaling, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  if (T < 0 || in_dim < 1 || out_total < 1) return fail(B200_LORA_EINVAL, "bad sizes T=%d in=%d out=%d", T, in_dim, out_total);
+  if (T == 0) return B200_LORA_OK;
+  if (y == nullptr || x == nullptr || weight == nullptr) return fail(B200_LORA_EINVAL, "null y / x / weight");
+  if (y_ld < out_total || x_ld < in_dim || w_ld < in_dim) return fail(B200_LORA_EINVAL, "row stride smaller than row");
+  LinearProblem lp;
+  lp.weight = weight; lp.w_ld = w_ld; lp.n_total = out_total; lp.bias = bias;
+  SliceTable st;
+  st.n = 0;
+  for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) { st.a[s] = st.b[s] = nullptr; st.out[s] = st.col[s] = 0; }
+  if (n_slices > 0 && token_to_slot != nullptr) {
+    if (S < 1 || r_max < 1) return fail(B200_LORA_EINVAL, "bad sizes S=%d r_max=%d", S, r_max);
+    if (out_sizes == nullptr || col_offsets == nullptr) return fail(B200_LORA_EINVAL, "null out_sizes / col_offsets");
+    if (int rc = fill_slices(st, n_slices, a_slabs, b_slabs, out_sizes, col_offsets, true, true)) return rc;
+    for (int s = 0; s < st.n; ++s)
+      if (st.col[s] + st.out[s] > out_total) return fail(B200_LORA_EINVAL, "slice %d exceeds the output width", s);
+  }
+  lp.lora.y = y; lp.lora.y_ld = y_ld; lp.lora.x = x; lp.lora.x_ld = x_ld; lp.lora.T = T; lp.lora.in_dim = in_dim;
+  lp.lora.S = S; lp.lora.r_max = r_max; lp.lora.st = st; lp.lora.scale_per_slot = scale_per_slot;
+  lp.lora.token_to_slot = token_to_slot; lp.lora.scaling = scaling;
+  return linear_lora_launch(lp, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
 size_t lora_b200_workspace_bytes(int32_t T, int32_t n_slices, int32_t r_max) {
   if (T < 0 || n_slices < 1 || r_max < 1) return 0;
   return sgmv_workspace_bytes(T, n_slices, r_max);
@@ -199,7 +228,7 @@ int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T,
     }
     case B200_LORA_IMPL_SGMV:
       if (dtype != B200_LORA_BF16) return fail(B200_LORA_EUNSUPPORTED, "prefill kernels are bf16 only");
-      return sgmv_launch(sp, workspace, workspace_bytes, st_);
+      return prefill_add_launch(sp, workspace, workspace_bytes, st_);
     default:
       return fail(B200_LORA_EUNSUPPORTED, "impl %d is not available", impl);
   }
@@ -339,7 +368,7 @@ int lora_b200_add_prefill_noalloc(void* y, int64_t y_ld, const void* x, int64_t 
   sp.st = st; sp.scale_per_slot = scale_per_slot; sp.token_to_slot = token_to_slot; sp.scaling = scaling;
   void* scratch = nullptr;
   if (int rc = static_scratch_for_current_device(&scratch)) return rc;
-  return sgmv_launch(sp, scratch, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
+  return prefill_add_launch(sp, scratch, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

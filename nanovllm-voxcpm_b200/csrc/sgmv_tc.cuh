@@ -33,6 +33,7 @@ struct SgmvArgs {
   const int32_t* token_to_slot;
   const float* scale_per_slot; float scaling;
   int zero_fill;                            // shrink: write zero rows for tokens without adapter
+  int skip_clean;                           // expand: leave blocks in which every row has an adapter to tc_tile_kernel
 };
 
 struct SgmvMaps {
@@ -239,7 +240,14 @@ sgmv_expand_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
   sgmv_find_runs(a.token_to_slot, a.T, a.S, blk, s_slot, run_slot, run_lo, run_hi, &nruns_s);
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
-  const int nruns = nruns_s;
+  int nruns = nruns_s;
+  {
+    // blocks in which every in-range row has an adapter are done by tc_tile_kernel when asked to
+    const int nvalid = min(kSgmvBM, a.T - blk * kSgmvBM);
+    int covered = 0;
+    for (int u = 0; u < nruns; ++u) covered += run_hi[u] - run_lo[u];
+    if (a.skip_clean && covered == nvalid) nruns = 0;
+  }
   const int row_bytes = r * 2;  // 32 / 64 / 128: the swizzle span of both operand tiles
 
   // Jobs of this CTA, in the same order for all three roles:

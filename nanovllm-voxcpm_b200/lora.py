@@ -180,6 +180,63 @@ def launch_add(
     N.check(rc)
 
 
+def fused_linear_supported(x: torch.Tensor, weight: torch.Tensor, r_max: int) -> bool:
+    """Shapes / dtypes the fused base-GEMM + LoRA kernel takes (bf16, in % 64 == 0, rank 16/32/64)."""
+    return (
+        x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
+        and x.size(1) % 64 == 0 and weight.size(0) % 8 == 0 and weight.stride(1) == 1 and x.stride(1) == 1
+        and r_max in (16, 32, 64)
+    )
+
+
+def linear_lora(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: torch.Tensor | None,
+    a_slabs: list[torch.Tensor],
+    b_slabs: list[torch.Tensor],
+    out_sizes: list[int],
+    col_offsets: list[int],
+    token_to_slot: torch.Tensor | None,
+    scaling: float = 1.0,
+    *,
+    scale_per_slot: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """``x @ weight.T (+ bias)`` plus the multi-LoRA delta in one pass over the output
+    (``lora_b200_linear_lora``): what the reference computes as ``F.linear`` followed by
+    ``add_lora`` (``layers/lora.py:341-366``). ``token_to_slot=None`` gives the plain linear."""
+    N.require_cuda(x, weight, bias, token_to_slot, *a_slabs, *b_slabs)
+    T, in_dim = x.shape
+    out_total = weight.size(0)
+    if out is None:
+        out = torch.empty((T, out_total), dtype=x.dtype, device=x.device)
+    if weight.size(1) != in_dim:
+        raise ValueError(f"weight input dim {weight.size(1)} does not match x features {in_dim}")
+    n = len(a_slabs) if token_to_slot is not None else 0
+    S = r_max = 1
+    workspace = None
+    if n:
+        S, r_max, a_in = a_slabs[0].shape
+        if a_in != in_dim:
+            raise ValueError(f"lora_A input dim {a_in} does not match x features {in_dim}")
+        if token_to_slot.dtype != torch.int32 or token_to_slot.numel() != T:
+            raise RuntimeError(
+                f"LoRA token_to_slot length does not match input rows: token_to_slot={token_to_slot.numel()} rows={T}"
+            )
+        workspace = scratch_for(x.device, N.workspace_bytes(T, n, r_max))
+    with torch.cuda.device(x.device):
+        rc = N.lib().lora_b200_linear_lora(
+            out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), T, in_dim, weight.data_ptr(), weight.stride(0),
+            out_total, N.ptr(bias), n, N.ptr_array(a_slabs[:n]) if n else None, N.ptr_array(b_slabs[:n]) if n else None,
+            N.int_array(out_sizes[:n]) if n else None, N.int_array(col_offsets[:n]) if n else None, S, r_max,
+            N.ptr(scale_per_slot), N.ptr(token_to_slot) if n else None, float(scaling), N.ptr(workspace),
+            0 if workspace is None else workspace.numel(), N.current_stream(x.device),
+        )
+    N.check(rc)
+    return out
+
+
 class B200LoRABackend:
     """``LoRABackend`` on hand-written sm_100a kernels (no Triton, no CPU path)."""
 
