@@ -32,6 +32,10 @@ from .distributed import get_tp_rank, get_tp_world_size
 from .lora import B200LoRABackend, LoRAMetadata, get_backend
 
 
+#: opt-in: route large bf16 batches through the fused base-GEMM + LoRA tensor-core kernel
+FUSED_LINEAR = False
+
+
 def _get_world_size() -> int:
     return get_tp_world_size()
 
@@ -121,6 +125,30 @@ class _LoRALayerBase(nn.Module):
             )
             context._cached_metadata = meta
         return meta  # type: ignore[return-value]
+
+    def _linear(self, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
+        """Base linear + LoRA delta of this module.
+
+        Default: cuBLAS (``F.linear``) followed by the fused in-place LoRA add. With
+        ``FUSED_LINEAR`` switched on, bf16 batches of at least ``lora.SGMV_MIN_TOKENS`` rows
+        take ``lora_b200_linear_lora`` instead: one tensor-core kernel whose accumulator
+        receives the delta before the single store of ``y``."""
+        if FUSED_LINEAR and x.is_cuda and isinstance(get_backend(), B200LoRABackend):
+            from .lora import SGMV_MIN_TOKENS, fused_linear_supported, linear_lora
+
+            x_flat = x if x.dim() == 2 else x.reshape(-1, x.size(-1))
+            if x_flat.size(0) >= SGMV_MIN_TOKENS and fused_linear_supported(x_flat, weight, self.max_lora_rank):
+                token_to_slot = self._resolve_token_slots(x_flat)
+                if token_to_slot is not None:
+                    widths, cols = self._slice_layout()
+                    active = [i for i, w in enumerate(widths) if w > 0]
+                    a, b = self._a_slices(), self._b_slices()
+                    y = linear_lora(
+                        x_flat, weight, bias, [a[i] for i in active], [b[i] for i in active],
+                        [widths[i] for i in active], [cols[i] for i in active], token_to_slot, 1.0,
+                    )
+                    return y if x.dim() == 2 else y.view(*x.shape[:-1], y.size(-1))
+        return self._apply_lora(F.linear(x, weight, bias), x)
 
     def _apply_lora(self, y: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
         """Add the LoRA delta of this module to ``y`` in place (fused shrink+expand)."""
@@ -326,7 +354,7 @@ class LoRAQKVParallelLinear(_LoRALayerBase):
         )
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self._apply_lora(F.linear(x, self.weight, self.bias), x)
+        return self._linear(x, self.weight, self.bias)
 
     def set_slot_lora(self, slot_id, lora_a, lora_b, effective_rank, scaling) -> None:
         self._write_slot(slot_id, list(lora_a), list(lora_b), effective_rank, scaling)
@@ -385,7 +413,7 @@ class LoRAMergedColumnParallelLinear(_LoRALayerBase):
         )
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self._apply_lora(F.linear(x, self.weight, self.bias), x)
+        return self._linear(x, self.weight, self.bias)
 
     def set_slot_lora(self, slot_id, lora_a, lora_b, effective_rank, scaling) -> None:
         self._write_slot(slot_id, list(lora_a), list(lora_b), effective_rank, scaling)
@@ -467,11 +495,11 @@ class LoRARowParallelLinear(_LoRALayerBase):
         return y
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        y = F.linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
+        bias = self.bias if self.tp_rank == 0 else None
         if self.lora_tp_mode == "allreduce_tmp":
-            y = self._apply_lora_allreduce_tmp(y, x)
+            y = self._apply_lora_allreduce_tmp(F.linear(x, self.weight, bias), x)
         else:
-            y = self._apply_lora(y, x)
+            y = self._linear(x, self.weight, bias)
         if self.tp_size > 1:
             dist.all_reduce(y)
         return y
@@ -517,7 +545,7 @@ class LoRALinear(_LoRALayerBase):
         return [self.out_features], [0]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self._apply_lora(F.linear(x, self.weight, self.bias), x)
+        return self._linear(x, self.weight, self.bias)
 
     def set_slot_lora(self, slot_id, lora_a, lora_b, effective_rank, scaling) -> None:
         self._write_slot(slot_id, [lora_a], [lora_b], effective_rank, scaling)

@@ -217,6 +217,8 @@ def linear_lora(
     S = r_max = 1
     workspace = None
     if n:
+        a_slabs = [_as_3d(a) for a in a_slabs]
+        b_slabs = [_as_3d(b) for b in b_slabs]
         S, r_max, a_in = a_slabs[0].shape
         if a_in != in_dim:
             raise ValueError(f"lora_A input dim {a_in} does not match x features {in_dim}")

@@ -418,3 +418,88 @@ def test_sgmv_unsupported_and_workspace_errors():
     with pytest.raises(RuntimeError, match="scratch"):
         LORA.launch_add(d.y, d.x, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets, meta, 1.0, impl=N.IMPL_SGMV, workspace=tiny)
     assert N.workspace_bytes(8192, 3, 64) >= 3 * 8192 * 64 * 2
+
+
+# ------------------------------------------------------------------ fused base GEMM + LoRA (tcgen05)
+def run_linear(p: W.Projection, bias=None, slots="own", **kw):
+    d = p.to_device(DEV)
+    tts = d.token_to_slot if slots == "own" else slots
+    out = LORA.linear_lora(d.x, d.weight, None if bias is None else bias.to(DEV), d.a_slabs, d.b_slabs,
+                           d.out_sizes, d.col_offsets, tts, 1.0, **kw)
+    torch.cuda.synchronize()
+    assert N.device_status(reset=True) == 0
+    return out
+
+
+@pytest.mark.parametrize("r_max,outs,bias", [(64, [512], False), (32, [256, 128, 128], True), (16, [384, 0, 128], True)])
+def test_fused_linear_lora_matches_oracle(r_max, outs, bias):
+    """One kernel computes x @ W.T (+ bias) and the LoRA delta; rows without adapter are
+    bit-identical to the same kernel run without any LoRA."""
+    lengths = [300, 128, 77, 1, 250, 140]  # T = 896: blocks with one slot, several slots and -1 holes
+    slots = []
+    for i, n in enumerate(lengths):
+        slots += [(i * 2) % 5] * n
+    p = W.make_projection(31 + r_max, len(slots), 1024, outs, 5, r_max, token_to_slot=slots, with_weight=True,
+                          ranks=[r_max, r_max // 2, r_max, 8, r_max])
+    p.token_to_slot[40:90] = -1
+    p.token_to_slot[600:603] = -1
+    gen = torch.Generator().manual_seed(5)
+    b = (torch.randn(sum(outs), generator=gen) * 0.5).to(torch.bfloat16) if bias else None
+    active = [i for i, w in enumerate(outs) if w > 0]
+    q = W.Projection(p.x, p.y, [p.a_slabs[i] for i in active], [p.b_slabs[i] for i in active],
+                     [outs[i] for i in active], [p.col_offsets[i] for i in active], p.ranks, p.token_to_slot, p.weight)
+    out = run_linear(q, b)
+    ref = O.linear_lora(q.x, q.weight, b, q.a_slabs, q.b_slabs, q.col_offsets, q.token_to_slot)
+    assert_lora_close(out, ref, max_abs=4e-2, what=f"fused linear r={r_max}")  # bf16 rounding of the base output included
+    plain = run_linear(q, b, slots=None)
+    assert_lora_close(plain, O.linear_lora(q.x, q.weight, b, None, None, None, None), max_abs=4e-2, what="plain linear")
+    none = (q.token_to_slot < 0).to(DEV)
+    assert torch.equal(out[none].view(torch.int16), plain[none].view(torch.int16)), "rows with slot -1 changed"
+    assert not torch.equal(out[~none], plain[~none])
+    again = run_linear(q, b)
+    assert torch.equal(out.view(torch.int16), again.view(torch.int16)), "two runs differ bitwise"
+
+
+def test_fused_linear_ragged_shapes_and_strides():
+    # T not a multiple of 128, out not a multiple of 256, padded row strides, caller-provided output
+    p = W.make_projection(9, 517, 320, [200, 120], 3, 32, with_weight=True, p_none=0.3)
+    d = p.to_device(DEV)
+    xp = torch.zeros(517, 320 + 64, dtype=torch.bfloat16, device=DEV)
+    xp[:, :320] = d.x
+    wp = torch.zeros(320, 320 + 8, dtype=torch.bfloat16, device=DEV)
+    wp[:, :320] = d.weight
+    out = torch.full((517, 320 + 16), 7.0, dtype=torch.bfloat16, device=DEV)
+    got = LORA.linear_lora(xp[:, :320], wp[:, :320], None, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets,
+                           d.token_to_slot, 1.0, out=out[:, :320])
+    torch.cuda.synchronize()
+    assert got.data_ptr() == out.data_ptr()
+    ref = O.linear_lora(p.x, p.weight, None, p.a_slabs, p.b_slabs, p.col_offsets, p.token_to_slot)
+    assert_lora_close(out[:, :320], ref, max_abs=4e-2, what="fused linear, ragged")
+    assert bool((out[:, 320:] == 7.0).all()), "columns beyond the output were written"
+
+
+def test_layers_take_fused_linear_when_switched_on(monkeypatch):
+    case = dict(kind="merged", hidden=512, outs=[768, 768], S=4, r=32)
+    torch.manual_seed(3)
+    layer = L.LoRAMergedColumnParallelLinear(case["hidden"], case["outs"], max_loras=4, max_lora_rank=32).to(DEV, torch.bfloat16)
+    layer.weight.data.normal_(0, 0.02)
+    for s in range(3):
+        a = torch.randn(2, 32, 512) * 0.05
+        bs = [torch.randn(768, 32) * 0.05, torch.randn(768, 32) * 0.05]
+        layer.set_slot_lora(s, a, bs, 32, 1.5)
+    T = 640
+    slots = torch.tensor(([0] * 200 + [-1] * 56 + [2] * 256 + [1] * 128), dtype=torch.int32)
+    x = torch.randn(T, 512).to(torch.bfloat16).to(DEV)
+    CTX.set_lora_context(CTX.build_lora_context_from_token_to_slot(slots.to(DEV)))
+    calls = []
+    real = LORA.linear_lora
+    monkeypatch.setattr(LORA, "linear_lora", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    with torch.no_grad():
+        unfused = layer(x)
+        assert not calls
+        monkeypatch.setattr(L, "FUSED_LINEAR", True)
+        fused = layer(x)
+        assert calls == [1]
+    torch.cuda.synchronize()
+    assert_lora_close(fused, unfused.float(), max_abs=4e-2, what="fused vs cuBLAS + add")
+    assert not torch.equal(fused[:200], (x[:200] @ layer.weight.T))
