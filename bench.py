@@ -58,6 +58,10 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default=None, choices=["qkv", "o", "gate_up", "down"],
+                    help="tuning: time one projection of every layer instead of all four")
+    ap.add_argument("--option", action="append", default=[], metavar="KEY=VALUE",
+                    help="tuning: lora_b200_set_option before the run (cluster, pdl, ring_kb, decode_kernel, smem_kb)")
     return ap.parse_args()
 
 
@@ -245,15 +249,23 @@ def run_gpu_arm(args):
     if not status.available:
         raise RuntimeError(f"B200 LoRA backend unavailable: {status.reason}")
 
+    option_keys = {"cluster": N.OPT_CLUSTER, "pdl": N.OPT_PDL, "ring_kb": N.OPT_RING_KB,
+                   "decode_kernel": N.OPT_DECODE_KERNEL, "smem_kb": N.OPT_SMEM_KB}
+    for item in args.option:
+        key, _, value = item.partition("=")
+        N.set_option(option_keys[key], int(value))
     slots, work = build_gpu_workload(device, args.layers)
+    if args.only:
+        work = [[p for p in layer if p["name"] == args.only] for layer in work]
     bufs = BP.GraphLoRABuffers.make(T_DECODE, N_SLOTS, device=device)
     bufs.load_plan(BP.build_lora_batch_plan_from_token_to_slot({}, slots.tolist()))
     ctx = bufs.context(T_DECODE)
     meta = LORA.LoRAMetadata(ctx.token_to_slot, ctx.token_indices_sorted_by_slot, ctx.active_slot_ids,
                              ctx.num_tokens_per_slot, ctx.slot_start_offsets, False, ctx.num_active_loras)
-    bytes_per_layer = sum(projection_bytes(slots, i, o) for i, o in W.DECODE_LAYER.values())
+    bytes_per_layer = sum(projection_bytes(slots, i, o) for k, (i, o) in W.DECODE_LAYER.items()
+                          if args.only in (None, k))
     bytes_per_step = bytes_per_layer * args.layers
-    launches_per_step = 4 * args.layers
+    launches_per_step = (1 if args.only else 4) * args.layers
 
     def step():
         for layer in work:

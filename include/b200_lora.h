@@ -193,6 +193,8 @@ size_t lora_b200_static_scratch_bytes(void);
 #define B200_LORA_OPT_CLUSTER 1 /* CTAs per slot bucket: 1, 2, 4, 8; 0 = choose from n_buckets */
 #define B200_LORA_OPT_PDL 2     /* 1 = launch with programmatic stream serialization (default), 0 = off */
 #define B200_LORA_OPT_RING_KB 3 /* cap of the shared-memory stage ring in KB, 0 = as large as fits */
+#define B200_LORA_OPT_DECODE_KERNEL 4 /* fused decode kernel: 0 = row-split, else column-split where only that takes the shape (default); 1 = row-split only; 2 = column-split only */
+#define B200_LORA_OPT_SMEM_KB 5 /* column-split kernel: cap of shared memory per CTA in KB, 0 = 112 (two CTAs per SM) */
 
 /* Sets a tuning knob; returns 0, or B200_LORA_EINVAL for an unknown key / value.
  * No counterpart in the reference (its tile configs are static tables,

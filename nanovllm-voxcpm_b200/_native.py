@@ -65,7 +65,8 @@ _SIGNATURES = {
     "lora_b200_device_status": (c_int32, [POINTER(c_int32), c_int32]),
 }
 
-OPT_CLUSTER, OPT_PDL, OPT_RING_KB = 1, 2, 3
+OPT_CLUSTER, OPT_PDL, OPT_RING_KB, OPT_DECODE_KERNEL, OPT_SMEM_KB = 1, 2, 3, 4, 5
+DECODE_AUTO, DECODE_ROW_SPLIT, DECODE_COLUMN_SPLIT = 0, 1, 2
 
 
 class NativeLibraryError(RuntimeError):

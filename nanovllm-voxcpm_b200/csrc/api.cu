@@ -3,6 +3,7 @@
 #include "common.cuh"
 #include "generic.cuh"
 #include "bgmv_fused.cuh"
+#include "bgmv_split.cuh"
 #include "sgmv_tc.cuh"
 #include "gemm_tc.cuh"
 
@@ -74,6 +75,9 @@ int launch_generic_expand(void* y, int64_t y_ld, const void* tmp, int T_rows, co
 
 }  // namespace
 
+// 0 = row-split kernel when it takes the shape, else the column-split one; 1 / 2 force one of them
+static int g_decode_kernel = 0;
+
 extern "C" {
 
 int lora_b200_version(void) { return B200_LORA_ABI_VERSION; }
@@ -94,6 +98,16 @@ int lora_b200_set_option(int32_t key, int32_t value) {
   if (key == B200_LORA_OPT_RING_KB) {
     if (value < 0 || value > 227) return fail(B200_LORA_EINVAL, "ring size %d KB outside [0, 227]", value);
     bgmv_options().ring_kb = value;
+    return B200_LORA_OK;
+  }
+  if (key == B200_LORA_OPT_DECODE_KERNEL) {
+    if (value < 0 || value > 2) return fail(B200_LORA_EINVAL, "decode kernel %d not in {0,1,2}", value);
+    g_decode_kernel = value;
+    return B200_LORA_OK;
+  }
+  if (key == B200_LORA_OPT_SMEM_KB) {
+    if (value < 0 || value > 227) return fail(B200_LORA_EINVAL, "shared-memory cap %d KB outside [0, 227]", value);
+    bgmv_split_options().smem_kb = value;
     return B200_LORA_OK;
   }
   return fail(B200_LORA_EINVAL, "unknown option %d", key);
@@ -203,7 +217,9 @@ int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T,
     if (dtype == B200_LORA_BF16 && T >= kSgmvAutoMinTokens && sgmv_supported(sp, nullptr) && workspace != nullptr &&
         workspace_bytes >= sgmv_workspace_bytes(T, n_act, r_max))
       impl = B200_LORA_IMPL_SGMV;
-    else if (dtype == B200_LORA_BF16 && have_buckets && bgmv_supported(bp, nullptr))
+    else if (dtype == B200_LORA_BF16 && have_buckets &&
+             (g_decode_kernel == 2 ? bgmv_split_supported(bp, nullptr)
+                                   : (bgmv_supported(bp, nullptr) || (g_decode_kernel == 0 && bgmv_split_supported(bp, nullptr)))))
       impl = B200_LORA_IMPL_BGMV;
     else
       impl = B200_LORA_IMPL_GENERIC;
@@ -223,8 +239,14 @@ int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T,
       if (dtype != B200_LORA_BF16) return fail(B200_LORA_EUNSUPPORTED, "fused decode kernel is bf16 only");
       if (!have_buckets) return fail(B200_LORA_EINVAL, "fused decode kernel needs the bucket arrays");
       const char* why = nullptr;
-      if (!bgmv_supported(bp, &why)) return fail(B200_LORA_EUNSUPPORTED, "fused decode kernel: %s", why);
-      return bgmv_launch(bp, st_);
+      if (g_decode_kernel == 2) {
+        if (!bgmv_split_supported(bp, &why)) return fail(B200_LORA_EUNSUPPORTED, "column-split decode kernel: %s", why);
+        return bgmv_split_launch(bp, st_);
+      }
+      if (bgmv_supported(bp, &why)) return bgmv_launch(bp, st_);
+      const char* why_split = nullptr;
+      if (g_decode_kernel == 0 && bgmv_split_supported(bp, &why_split)) return bgmv_split_launch(bp, st_);
+      return fail(B200_LORA_EUNSUPPORTED, "fused decode kernel: %s", why);
     }
     case B200_LORA_IMPL_SGMV:
       if (dtype != B200_LORA_BF16) return fail(B200_LORA_EUNSUPPORTED, "prefill kernels are bf16 only");

@@ -29,6 +29,8 @@ def _clean():
     yield
     N.set_option(N.OPT_CLUSTER, 0)
     N.set_option(N.OPT_PDL, 1)
+    N.set_option(N.OPT_DECODE_KERNEL, N.DECODE_AUTO)
+    N.set_option(N.OPT_SMEM_KB, 0)
     CTX.reset_lora_context()
     assert N.device_status() == 0, "a kernel gave up a bounded wait"
 
@@ -106,6 +108,50 @@ def test_bgmv_cluster_sizes(cluster, pdl):
         p = W.decode_projection(name, seed=3, T=96, S=8)
         out, y_in = run_add(p, N.IMPL_BGMV, "graph")
         check_against_oracle(p, out, y_in, what=f"{name}/C{cluster}/pdl{pdl}")
+
+
+@pytest.mark.parametrize("cluster", [0, 1, 2, 8])
+@pytest.mark.parametrize("smem_kb", [0, 227])
+def test_column_split_decode_kernel(cluster, smem_kb):
+    """The second fused decode kernel (input columns split over the cluster, st.async exchange,
+    two CTAs per SM): same contract, same oracle, every projection shape and bucket convention."""
+    N.set_option(N.OPT_DECODE_KERNEL, N.DECODE_COLUMN_SPLIT)
+    N.set_option(N.OPT_CLUSTER, cluster)
+    N.set_option(N.OPT_SMEM_KB, smem_kb)
+    for name, convention in (("qkv", "graph"), ("o", "eager"), ("gate_up", "vllm"), ("down", "graph")):
+        if cluster == 8 and name == "qkv":
+            continue  # 8 receive buffers of 96 rank rows exceed the shared memory of one CTA
+        p = W.decode_projection(name, seed=11)
+        out, y_in = run_add(p, N.IMPL_BGMV, convention)
+        check_against_oracle(p, out, y_in, what=f"column-split/{name}/C{cluster}")
+        out2, _ = run_add(p, N.IMPL_BGMV, convention)
+        assert torch.equal(out.view(torch.int16), out2.view(torch.int16)), "two runs differ bitwise"
+    # 7 passes of 16 tokens per bucket (receive buffer reused under the peers' free signal), one token,
+    # ragged widths, rank 128 with a rank array, scales
+    p = W.make_projection(5, 200, 1024, [1024, 128, 128], 2, 32, p_none=0.2)
+    out, y_in = run_add(p, N.IMPL_BGMV)
+    check_against_oracle(p, out, y_in, what="column-split/many tokens")
+    p = W.make_projection(6, 1, 1024, [1024], 4, 32, token_to_slot=[3])
+    out, y_in = run_add(p, N.IMPL_BGMV)
+    check_against_oracle(p, out, y_in, what="column-split/one token")
+    p = W.make_projection(11, 37, 1312, [200, 40], 3, 32)
+    out, y_in = run_add(p, N.IMPL_BGMV, y_pad=8, x_pad=16)
+    check_against_oracle(p, out, y_in, what="column-split/ragged")
+    if cluster != 8:
+        sps = torch.tensor([1.0, 0.5, 2.0])
+        p = W.make_projection(12, 40, 512, [512], 3, 128, ranks=[128, 40, 8])
+        out, y_in = run_add(p, N.IMPL_BGMV, use_ranks=True, scaling=0.5, scale_per_slot=sps)
+        check_against_oracle(p, out, y_in, 0.5, sps, what="column-split/r128")
+
+
+def test_column_split_unsupported_shapes_fall_back_or_report():
+    p = W.make_projection(9, 70, 2048, [2048, 256, 256], 6, 64, p_none=0.15)  # 3 slices x rank 64: 6 row boxes
+    N.set_option(N.OPT_DECODE_KERNEL, N.DECODE_COLUMN_SPLIT)
+    with pytest.raises(RuntimeError, match="column-split"):
+        run_add(p, N.IMPL_BGMV)
+    N.set_option(N.OPT_DECODE_KERNEL, N.DECODE_AUTO)
+    out, y_in = run_add(p, N.IMPL_BGMV)
+    check_against_oracle(p, out, y_in, what="auto picks the row-split kernel")
 
 
 def test_bgmv_many_tokens_per_slot_and_single_token():
