@@ -58,6 +58,9 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "linear"],
+                    help="decode = the headline decode BGMV layer; prefill = prefill SGMV add (tcgen05 kernels) of one "
+                         "layer; linear = base GEMM + LoRA in one tensor-core kernel for the same layer")
     ap.add_argument("--only", default=None, choices=["qkv", "o", "gate_up", "down"],
                     help="tuning: time one projection of every layer instead of all four")
     ap.add_argument("--option", action="append", default=[], metavar="KEY=VALUE",
@@ -400,10 +403,125 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------ secondary workloads (prefill kernels)
+def run_prefill_arm(args):
+    """One step = the four multi-LoRA projections of one prefill layer (16 requests, <= 8192 rows, hidden 2048,
+    intermediate 6144, ranks 8/16/64 in a rank-64 slab). `prefill`: y += delta through lora_b200_add
+    (tcgen05 shrink + tile / run expand), HBM-bound. `linear`: y = x W^T + delta through lora_b200_linear_lora,
+    tensor-bound; cuBLAS + the prefill add is timed beside it. Inputs of one layer (> 0.6 GB) exceed L2."""
+    from nanovllm_voxcpm_b200 import _native as N
+    from nanovllm_voxcpm_b200 import batch_plan as BP
+    from nanovllm_voxcpm_b200 import lora as LORA
+    from nanovllm_voxcpm_b200 import workloads as W
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise RuntimeError("--workload prefill / linear are single-GPU measurements")
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    names = [args.only] if args.only else list(W.PREFILL_LAYER)
+    sets = []
+    for k in range(2):  # two independent layer sets, alternated
+        layer = []
+        for name in names:
+            p = W.prefill_projection(name, seed=k)
+            gen = torch.Generator().manual_seed(100 + k)
+            p.weight = (torch.randn(sum(p.out_sizes), p.x.shape[1], generator=gen) * 0.02).to(torch.bfloat16)
+            layer.append((name, p, p.to_device(device)))
+        sets.append(layer)
+    metas = {}
+    for name, p, d in sets[0] + sets[1]:
+        ctx = BP.build_lora_context_from_batch_plan(
+            BP.build_lora_batch_plan_from_token_to_slot({}, p.token_to_slot.tolist()), device=device)
+        metas[id(d)] = LORA.LoRAMetadata(ctx.token_to_slot, ctx.token_indices_sorted_by_slot, ctx.active_slot_ids,
+                                         ctx.num_tokens_per_slot, ctx.slot_start_offsets, False, ctx.num_active_loras)
+    T = sets[0][0][1].x.shape[0]
+    linear = args.workload == "linear"
+    outs = {id(d): torch.empty_like(d.y) for layer in sets for _, _, d in layer}
+
+    def launch(d):
+        if linear:
+            LORA.linear_lora(d.x, d.weight, None, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets, d.token_to_slot, 1.0,
+                             out=outs[id(d)])
+        else:
+            LORA.launch_add(d.y, d.x, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets, metas[id(d)], 1.0, impl=N.IMPL_SGMV)
+
+    def unfused(d):
+        y = torch.mm(d.x, d.weight.t(), out=outs[id(d)])  # cuBLAS into a preallocated output
+        LORA.launch_add(y, d.x, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets, metas[id(d)], 1.0, impl=N.IMPL_SGMV)
+
+    def timed(fn, reps):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        for i in range(reps):
+            fn(i)
+        e.record()
+        e.synchronize()
+        return s.elapsed_time(e) / reps
+
+    step = lambda i: [launch(d) for _, _, d in sets[i & 1]]  # noqa: E731
+    for i in range(max(3, args.warmup)):
+        step(i)
+    sampler = ClockSampler(0)
+    sampler.start()
+    t_wall = time.perf_counter()
+    ms_per_step = timed(step, args.steps)
+    while time.perf_counter() - t_wall < 0.6:
+        step(0)
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    per_proj = {}
+    for j, name in enumerate(names):
+        per_proj[name] = timed(lambda i, j=j: launch(sets[i & 1][j][2]), max(args.steps, 10)) * 1e3
+    bytes_step = sum(W.algorithmic_bytes(p) for _, p, _ in sets[0])
+    lora_flops = 0
+    for _, p, _ in sets[0]:
+        r_tok = p.ranks[p.token_to_slot.clamp(min=0).long()] * (p.token_to_slot >= 0)
+        lora_flops += int(r_tok.sum()) * 2 * (len(p.out_sizes) * p.x.shape[1] + sum(p.out_sizes))
+    base_flops = sum(2 * T * p.x.shape[1] * sum(p.out_sizes) for _, p, _ in sets[0])
+    hbm_peak, kind = measured_peak()
+    line = {"n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"prefill layer: 16 requests, T={T} rows, hidden 2048, intermediate 6144, 16 adapters "
+                                   f"ranks 8/16/64 in a rank-64 slab; projections {'+'.join(names)}",
+                       "cache_defeat": "inputs larger than L2 (two layer sets of > 0.6 GB alternated)"},
+            "us_per_projection": per_proj, "clocks": clocks, "device_status": N.device_status()}
+    if linear:
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                tf_peak, tkind = float(json.load(f)["bf16_tflops"]), "measured burst"
+        except Exception:
+            tf_peak, tkind = 1590.0, "fallback"
+        for i in range(3):  # cuBLAS handle / heuristics outside the timed region
+            [unfused(d) for _, _, d in sets[i & 1]]
+        unf = timed(lambda i: [unfused(d) for _, _, d in sets[i & 1]], max(3, args.steps // 2))
+        ach = (base_flops + lora_flops) / (ms_per_step * 1e-3) / 1e12
+        line.update({"metric": "fused base GEMM + multi-LoRA TFLOP/s (prefill layer, algorithmic flops)", "value": ach,
+                     "unit": "TFLOP/s", "gpu_launches": 2 * len(names) * args.steps,
+                     "roofline": {"bound": "tensor", "achieved": ach, "peak": tf_peak, "unit": "TFLOP/s",
+                                  "frac": ach / tf_peak, "traffic": None, "peak_kind": f"of {tkind}",
+                                  "kernel": "tc_tile_kernel", "algorithmic_flops_per_step": base_flops + lora_flops},
+                     "cublas_plus_prefill_add_ms_per_step": unf})
+    else:
+        ach = bytes_step / (ms_per_step * 1e-3) / 1e9
+        line.update({"metric": "multi-LoRA linear GB/s (prefill SGMV, algorithmic bytes)", "value": ach, "unit": "GB/s",
+                     "gpu_launches": 2 * len(names) * args.steps,
+                     "roofline": {"bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
+                                  "traffic": None, "peak_kind": f"of {kind}",
+                                  "kernel": "sgmv_shrink_kernel + tc_tile_kernel",
+                                  "algorithmic_bytes_per_step": bytes_step},
+                     "lora_tflops": lora_flops / (ms_per_step * 1e-3) / 1e12})
+    print(json.dumps(line))
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload != "decode":
+        run_prefill_arm(args)
     else:
         run_gpu_arm(args)
 

@@ -15,9 +15,9 @@
 // Rows of a block may use different slots (request boundaries): the mask warp zeroes, in the
 // shared-memory copy of tmp, the rows that do not belong to the run whose B is being
 // multiplied, so every row only receives its own adapter's delta. Rows without adapter get a
-// zero delta: exact in LINEAR mode (y is stored, the base result is unchanged); in EXPAND mode
-// adding +0.0 could flip a -0.0, so blocks that contain such rows are left to the run-based
-// expand kernel of sgmv_tc.cuh, which never touches them.
+// zero delta: exact in LINEAR mode (y is stored, the base result is unchanged). In EXPAND mode
+// their staged delta is NEGATIVE zero: x + (-0.0) == x bit for bit for every x, both zeros and
+// denormals included (the reduce-add does not flush), whereas +0.0 would turn a -0.0 into +0.0.
 #pragma once
 
 #include "sgmv_tc.cuh"
@@ -25,6 +25,7 @@
 namespace b200lora {
 
 constexpr int kTileThreads = 224;  // warp 0 TMA, warp 1 MMA + TMEM owner, warps 2-5 epilogue, warp 6 row mask
+constexpr int kTileSMs = 148;      // SMs of a B200: the schedule below is sized for them
 constexpr int kGemmStages = 3;
 constexpr int kGemmStageBytes = kSgmvBM * kSgmvBK * 2 + kSgmvBN * kSgmvBK * 2;  // 48 KB: x tile + W tile
 constexpr int kGemmOutChunk = 64;                                               // columns per TMA store box
@@ -113,8 +114,8 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
-  // EXPAND mode only takes blocks in which every row has an adapter (see the header comment)
-  const bool active = !a.expand_mode || (clean_s != 0 && nruns_s > 0);
+  // EXPAND mode has nothing to add to a block without any adapter row
+  const bool active = !a.expand_mode || nruns_s > 0;
   const int nruns = active ? nruns_s : 0;
   const int ntile = active ? (a.n_total + kSgmvBN - 1) / kSgmvBN : 0;
   const int nk = a.expand_mode ? 0 : a.in_dim / kSgmvBK;
@@ -237,6 +238,8 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
     const int quarter = warp & 3;
     const int row_in_blk = quarter * 32 + lane;
     const int etid = tid - 64;  // 0..127
+    // EXPAND mode: this thread's row has no adapter -> its delta is -0.0 (see the header comment)
+    const bool neg_zero_row = a.expand_mode && s_slot[row_in_blk] < 0;
     int job = 0, chunk_no = 0;
     for (int j = z; j < ntile; j += Z, ++job) {
       const int buf = job & 1;
@@ -269,6 +272,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
             o.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
             o.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
             o.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+            if (neg_zero_row) o = make_uint4(0x80008000u, 0x80008000u, 0x80008000u, 0x80008000u);
             // 128-byte swizzle of the TMA box: 16-byte chunk index XOR (row % 8)
             const uint32_t chunk16 = (uint32_t)(4 * h + q) ^ (uint32_t)(row_in_blk & 7);
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(obuf + (uint32_t)row_in_blk * 128u + chunk16 * 16u),
@@ -342,14 +346,22 @@ inline int tc_tile_launch(const GemmMaps& maps, const GemmArgs& a, cudaStream_t 
   if (int rc = sgmv_set_smem(reinterpret_cast<const void*>(tc_tile_kernel), smem)) return rc;
   const int nblk = (a.T + kSgmvBM - 1) / kSgmvBM;
   const int ntile = (a.n_total + kSgmvBN - 1) / kSgmvBN;
-  const int Z = std::max(1, std::min(ntile, (148 + nblk - 1) / nblk));
+  // Column tiles of a row block are dealt to Z CTAs. One CTA fits per SM, so the grid runs in
+  // ceil(nblk * Z / SMs) rounds of ceil(ntile / Z) tiles each; pick the Z with the shortest schedule
+  // (half a tile charged per round for the prologue of a CTA).
+  int Z = 1;
+  double best = 1e30;
+  for (int z = 1; z <= ntile; ++z) {
+    const int rounds = (nblk * z + kTileSMs - 1) / kTileSMs;
+    const double cost = rounds * ((ntile + z - 1) / z + 0.5);
+    if (cost < best - 1e-9) { best = cost; Z = z; }
+  }
   tc_tile_kernel<<<dim3(nblk, Z), kTileThreads, smem, stream>>>(maps, a);
   return check_launch("tc_tile_kernel");
 }
 
-// y += LoRA delta for a prefill batch: shrink, then the reduce-add tile kernel for blocks in which
-// every row has an adapter and the run-based expand for the rest (or the run-based expand alone
-// when the slices do not tile the output in 64-column units).
+// y += LoRA delta for a prefill batch: shrink, then the reduce-add tile kernel (or the run-based
+// expand when the slices do not tile the output in 64-column units).
 inline int prefill_add_launch(const SgmvProblem& b, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   SgmvMaps sm;
   SgmvArgs sa;
@@ -361,8 +373,7 @@ inline int prefill_add_launch(const SgmvProblem& b, void* workspace, size_t work
     GemmMaps gm;
     GemmArgs ga;
     if (int rc = tc_tile_prepare(sm, sa, nullptr, 0, n_total, nullptr, true, true, &gm, &ga)) return rc;
-    if (int rc = tc_tile_launch(gm, ga, stream)) return rc;
-    sa.skip_clean = 1;
+    return tc_tile_launch(gm, ga, stream);
   }
   return sgmv_launch_expand(sm, sa, stream);
 }

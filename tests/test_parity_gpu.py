@@ -410,6 +410,10 @@ def test_prefill_projection_matches_oracle(name):
     tensor-core kernels vs oracle; rows of a request boundary share a 128-row block."""
     p = W.prefill_projection(name, seed=3, lengths=[200, 77, 133, 128, 64])
     p.token_to_slot[10:25] = -1  # a hole without adapter inside the first request
+    # bit patterns that an "add zero" would destroy: -0.0, a bf16 denormal, the largest finite value
+    p.y[10:25, 0::3] = -0.0
+    p.y[10:25, 1::3] = torch.tensor(1e-40).to(torch.bfloat16)
+    p.y[12, 5] = torch.finfo(torch.bfloat16).max
     out, y_in = run_add(p, N.IMPL_SGMV)
     check_against_oracle(p, out, y_in, what=f"sgmv/{name}")
     out2, _ = run_add(p, N.IMPL_SGMV)
