@@ -53,7 +53,10 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-gpu"],
+                    help="b200 = this library; reference = the CPU restatement of the reference's op on the host cores; "
+                         "reference-gpu = the unmodified reference's own GPU backend (its Triton kernels) from "
+                         "baseline/_ref on the same workload, where that install and triton are usable")
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
@@ -516,10 +519,119 @@ def run_prefill_arm(args):
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------ the reference's own GPU backend
+def run_reference_gpu_arm(args):
+    """Times `get_backend().add_lora` of the UNMODIFIED reference package (installed from its source tree into
+    baseline/_ref; nothing of this library on the path) on the decode or prefill workload of this file, eagerly
+    and, for decode, inside a CUDA graph exactly as its runner replays it. Prints one JSON line."""
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    try:
+        if not os.path.isdir(os.path.join(ref_root, "nanovllm_voxcpm")):
+            raise RuntimeError("baseline/_ref holds no install of the reference")
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device")
+        sys.path.insert(0, ref_root)
+        import nanovllm_voxcpm.lora as RL
+
+        status = RL.get_availability()
+        if not status.available:
+            raise RuntimeError(f"reference backend unavailable: {status.reason}")
+        backend = RL.get_backend()
+    except Exception as exc:
+        print(json.dumps({"impl": "reference-gpu", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}))
+        return
+    from nanovllm_voxcpm_b200 import batch_plan as BP
+    from nanovllm_voxcpm_b200 import workloads as W
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    decode = args.workload == "decode"
+    if decode:
+        slots, work = build_gpu_workload(device, args.layers)
+        bufs = BP.GraphLoRABuffers.make(T_DECODE, N_SLOTS, device=device)
+        bufs.load_plan(BP.build_lora_batch_plan_from_token_to_slot({}, slots.tolist()))
+        ctx = bufs.context(T_DECODE)
+        if args.only:
+            work = [[p for p in layer if p["name"] == args.only] for layer in work]
+        bytes_step = sum(projection_bytes(slots, i, o) for k, (i, o) in W.DECODE_LAYER.items()
+                         if args.only in (None, k)) * args.layers
+        meta = RL.LoRAMetadata(ctx.token_to_slot, ctx.token_indices_sorted_by_slot, ctx.active_slot_ids,
+                               ctx.num_tokens_per_slot, ctx.slot_start_offsets, False, ctx.num_active_loras)
+        metas = None
+    else:
+        names = [args.only] if args.only else list(W.PREFILL_LAYER)
+        work, metas, bytes_step = [], {}, 0
+        for k in range(2):
+            layer = []
+            for name in names:
+                p = W.prefill_projection(name, seed=k)
+                d = p.to_device(device)
+                c = BP.build_lora_context_from_batch_plan(
+                    BP.build_lora_batch_plan_from_token_to_slot({}, p.token_to_slot.tolist()), device=device)
+                item = dict(name=name, x=d.x, y=d.y, a=d.a_slabs, b=d.b_slabs, outs=list(d.out_sizes))
+                metas[id(item)] = RL.LoRAMetadata(c.token_to_slot, c.token_indices_sorted_by_slot, c.active_slot_ids,
+                                                  c.num_tokens_per_slot, c.slot_start_offsets, False, c.num_active_loras)
+                layer.append(item)
+                if k == 0:
+                    bytes_step += W.algorithmic_bytes(p)
+            work.append(layer)
+        meta = None
+
+    def step(i=None):
+        layers = work if decode else [work[(i or 0) & 1]]
+        for layer in layers:
+            for p in layer:
+                m = meta if decode else metas[id(p)]
+                backend.add_lora(list(p["y"].split(p["outs"], dim=-1)), p["x"], p["a"], p["b"],
+                                 indices=m.token_to_slot, metadata=m, scaling=1.0, y_packed=p["y"])
+
+    stream = torch.cuda.Stream(device)
+    mode = "eager"
+    with torch.inference_mode(), torch.cuda.stream(stream):
+        for i in range(max(3, args.warmup)):  # Triton compiles and autotunes here
+            step(i)
+        stream.synchronize()
+        run = step
+        if decode and not args.no_graph:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    step()
+                run = lambda i=None: graph.replay()  # noqa: E731
+                mode = "cuda_graph"
+            except Exception as exc:
+                mode = f"eager (graph capture failed: {type(exc).__name__})"
+                torch.cuda.synchronize()
+        for i in range(3):
+            run(i)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream.synchronize()
+        s.record(stream)
+        for i in range(args.steps):
+            run(i)
+        e.record(stream)
+        e.synchronize()
+    ms = s.elapsed_time(e) / args.steps
+    value = bytes_step / (ms * 1e-3) / 1e9
+    nproj = sum(len(layer) for layer in work) if decode else len(work[0])
+    print(json.dumps({
+        "impl": "reference-gpu", "metric": METRIC if decode else "multi-LoRA linear GB/s (prefill SGMV, algorithmic bytes)",
+        "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": config_dict(args.layers) if decode else {"workload": "prefill layer (see --workload prefill)"},
+        "launch_mode": mode, "us_per_projection_call": ms * 1e3 / nproj,
+        "backend": type(backend).__name__,
+    }))
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu_arm(args)
     elif args.workload != "decode":
         run_prefill_arm(args)
     else:
