@@ -189,6 +189,30 @@ int lora_b200_add_prefill_noalloc(void* y, int64_t y_ld, const void* x, int64_t 
  * the reference. */
 size_t lora_b200_static_scratch_bytes(void);
 
+/* conventions of lora_b200_build_metadata */
+#define B200_LORA_META_GRAPH 0  /* fixed buckets [-1, 0 .. S-1], bucket 0 always empty (CUDA-graph buffers) */
+#define B200_LORA_META_KERNEL 1 /* compact ids incl. the -1 bucket with its rows (LoRAKernelMeta.prepare_tensors) */
+#define B200_LORA_META_EAGER 2  /* compact ids of the slots >= 0 that occur (eager batch plan) */
+
+/*
+ * Builds the step's index metadata from token_to_slot on the device, in one launch: the stable
+ * order of token rows by slot, rows per bucket and bucket start offsets. Same integers, bit for
+ * bit, as the reference builds on the host with loops over the tokens and then copies over:
+ * `build_lora_batch_plan_from_token_to_slot` (nanovllm_voxcpm/engine/lora_manager.py:77-111) for
+ * EAGER, `_copy_lora_domain_to_graph_vars` (engine/model_runner.py:774-797) for GRAPH,
+ * `LoRAKernelMeta.prepare_tensors` (lora_ops/triton_ops/lora_kernel_metadata.py:47-67) for KERNEL.
+ *  token_to_slot device int32[T]; ids outside [-1, S) count as -1 and are reported in info[2]
+ *  sorted_idx    device int32[>= T]; GRAPH / EAGER write the rows with an adapter (the tail keeps
+ *                its old content), KERNEL writes all T rows
+ *  slot_ids      device int32[S+1]; may be NULL for GRAPH (the ids are the constants -1 .. S-1)
+ *  counts        device int32[S+1];  offsets device int32[S+2]
+ *  info          device int32[3] or NULL: buckets in use, rows with an adapter, rows with a bad id
+ * T <= 16384, 1 <= S <= 4095.
+ */
+int lora_b200_build_metadata(const int32_t* token_to_slot, int32_t T, int32_t S, int32_t convention,
+                             int32_t* sorted_idx, int32_t* slot_ids, int32_t* counts, int32_t* offsets,
+                             int32_t* info, void* stream);
+
 /* Tuning knobs of the fused decode kernel (process-wide, read at launch time). */
 #define B200_LORA_OPT_CLUSTER 1 /* CTAs per slot bucket: 1, 2, 4, 8; 0 = choose from n_buckets */
 #define B200_LORA_OPT_PDL 2     /* 1 = launch with programmatic stream serialization (default), 0 = off */

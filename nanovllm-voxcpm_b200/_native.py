@@ -61,12 +61,16 @@ _SIGNATURES = {
          POINTER(c_int32), POINTER(c_int32), c_int32, c_int32, c_void_p, c_void_p, c_float, c_void_p],
     ),
     "lora_b200_static_scratch_bytes": (c_size_t, []),
+    "lora_b200_build_metadata": (
+        c_int32, [c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    ),
     "lora_b200_set_option": (c_int32, [c_int32, c_int32]),
     "lora_b200_device_status": (c_int32, [POINTER(c_int32), c_int32]),
 }
 
 OPT_CLUSTER, OPT_PDL, OPT_RING_KB, OPT_DECODE_KERNEL, OPT_SMEM_KB = 1, 2, 3, 4, 5
 DECODE_AUTO, DECODE_ROW_SPLIT, DECODE_COLUMN_SPLIT = 0, 1, 2
+META_GRAPH, META_KERNEL, META_EAGER = 0, 1, 2
 
 
 class NativeLibraryError(RuntimeError):
@@ -158,6 +162,23 @@ def device_status(reset: bool = False) -> int:
     out = c_int32(0)
     check(lib().lora_b200_device_status(ctypes.byref(out), 1 if reset else 0))
     return out.value
+
+
+def build_metadata(token_to_slot, S: int, convention: int, sorted_idx, slot_ids, counts, offsets, info=None) -> None:
+    """``lora_b200_build_metadata`` on the current stream: index arrays of the step from the device-resident
+    slot map, without host loops or copies (arrays as documented in include/b200_lora.h)."""
+    require_cuda(token_to_slot, sorted_idx, slot_ids, counts, offsets, info)
+    for name, t in (("token_to_slot", token_to_slot), ("sorted_idx", sorted_idx), ("slot_ids", slot_ids),
+                    ("counts", counts), ("offsets", offsets), ("info", info)):
+        if t is not None and (t.dtype != torch.int32 or not t.is_contiguous()):
+            raise ValueError(f"{name} must be a contiguous int32 tensor")
+    T = token_to_slot.numel()
+    if sorted_idx.numel() < T or counts.numel() < S + 1 or offsets.numel() < S + 2 or \
+            (slot_ids is not None and slot_ids.numel() < S + 1) or (info is not None and info.numel() < 3):
+        raise ValueError("metadata arrays are too small for T rows and S slots")
+    with torch.cuda.device(token_to_slot.device):
+        check(lib().lora_b200_build_metadata(ptr(token_to_slot), T, S, convention, ptr(sorted_idx), ptr(slot_ids),
+                                             ptr(counts), ptr(offsets), ptr(info), current_stream(token_to_slot.device)))
 
 
 def workspace_bytes(T: int, n_slices: int, r_max: int) -> int:

@@ -147,6 +147,22 @@ class GraphLoRABuffers:
         self.num_tokens_per_slot.copy_(views[2], non_blocking=True)
         self.slot_start_offsets.copy_(views[3], non_blocking=True)
 
+    def load_token_to_slot_on_device(self, token_to_slot: torch.Tensor) -> None:
+        """Same buffers as :meth:`load_plan`, built on the GPU from a device-resident slot map in two
+        launches (a copy and ``lora_b200_build_metadata``): no Python loop over the rows, no staging
+        copy, nothing to synchronise. Slot ids outside the graph slots count as "no adapter"."""
+        from . import _native as N
+
+        n = token_to_slot.numel()
+        rows = self.token_to_slot.numel()
+        if n > rows:
+            raise ValueError(f"slot map has {n} rows, graph buffers hold {rows}")
+        self.token_to_slot[:n].copy_(token_to_slot, non_blocking=True)
+        if n < rows:
+            self.token_to_slot[n:].fill_(-1)
+        N.build_metadata(self.token_to_slot, self.num_buckets - 1, N.META_GRAPH, self.token_indices_sorted_by_slot,
+                         None, self.num_tokens_per_slot, self.slot_start_offsets)
+
     def context(self, token_count: int, no_lora_flag: bool = False) -> LoRAContext:
         return LoRAContext(
             token_to_slot=self.token_to_slot[:token_count],

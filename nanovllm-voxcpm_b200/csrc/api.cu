@@ -4,6 +4,7 @@
 #include "generic.cuh"
 #include "bgmv_fused.cuh"
 #include "bgmv_split.cuh"
+#include "metadata.cuh"
 #include "sgmv_tc.cuh"
 #include "gemm_tc.cuh"
 
@@ -111,6 +112,13 @@ int lora_b200_set_option(int32_t key, int32_t value) {
     return B200_LORA_OK;
   }
   return fail(B200_LORA_EINVAL, "unknown option %d", key);
+}
+
+int lora_b200_build_metadata(const int32_t* token_to_slot, int32_t T, int32_t S, int32_t convention,
+                             int32_t* sorted_idx, int32_t* slot_ids, int32_t* counts, int32_t* offsets,
+                             int32_t* info, void* stream) {
+  return build_metadata(token_to_slot, T, S, convention, sorted_idx, slot_ids, counts, offsets, info,
+                        static_cast<cudaStream_t>(stream));
 }
 
 #ifdef B200_TRACE

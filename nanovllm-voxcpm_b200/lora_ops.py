@@ -189,6 +189,21 @@ class LoRAKernelMeta:
                 k = self.captured_lora_counts[pos]
         self.num_active_loras = k
 
+    def prepare_tensors_on_device(self, token_lora_mapping: torch.Tensor) -> None:
+        """:meth:`prepare_tensors` in one kernel launch (``lora_b200_build_metadata``), without sort /
+        unique / cumsum launches and without a host read: ``no_lora_flag`` stays False and
+        ``num_active_loras`` the buffer capacity, which every kernel of this package accepts (empty and
+        ``-1`` buckets exit at once)."""
+        from . import _native as N
+
+        n = token_lora_mapping.numel()
+        self.token_lora_mapping[:n].copy_(token_lora_mapping, non_blocking=True)
+        N.build_metadata(self.token_lora_mapping[:n], self.active_lora_ids.numel() - 1, N.META_KERNEL,
+                         self.token_indices_sorted_by_lora_ids, self.active_lora_ids, self.num_tokens_per_lora,
+                         self.lora_token_start_loc)
+        self.no_lora_flag = False
+        self.num_active_loras = self.default_num_active_loras
+
     def meta_args(self, token_nums: int, specialize_active_lora: bool):
         active = self.num_active_loras if specialize_active_lora else self.default_num_active_loras
         return (

@@ -553,3 +553,84 @@ def test_layers_take_fused_linear_when_switched_on(monkeypatch):
     torch.cuda.synchronize()
     assert_lora_close(fused, unfused.float(), max_abs=4e-2, what="fused vs cuBLAS + add")
     assert not torch.equal(fused[:200], (x[:200] @ layer.weight.T))
+
+
+# ------------------------------------------------------------------ device-side metadata build
+def _random_map(seed, T, S, p_none):
+    gen = torch.Generator().manual_seed(seed)
+    return W.uniform_slots(gen, T, S, p_none)
+
+
+@pytest.mark.parametrize("T,S,p_none", [(1, 4, 0.0), (256, 32, 0.1), (777, 5, 0.5), (1024, 128, 0.02), (4096, 16, 0.3),
+                                        (8172, 16, 0.0), (16384, 1024, 0.1), (300, 4095, 0.2), (64, 8, 1.0)])
+def test_device_metadata_build_is_bit_identical_to_the_host_builders(T, S, p_none):
+    slots = _random_map(T + S, T, S, p_none)
+    if T == 8172:  # prefill layout: contiguous requests, one slot each
+        slots = W.prefill_projection("o", seed=0).token_to_slot
+    dev = slots.to(DEV)
+    # --- graph buffers (stale tail of the sorted buffer must stay as it was)
+    rows = min(T + 7, 16384)  # buffers longer than the step, as the runner's are
+    host = BP.GraphLoRABuffers.make(rows, S, device=DEV)
+    host.load_plan(BP.build_lora_batch_plan_from_token_to_slot({}, slots.tolist()))
+    mine = BP.GraphLoRABuffers.make(rows, S, device=DEV)
+    mine.load_token_to_slot_on_device(dev)
+    torch.cuda.synchronize()
+    for name in ("token_to_slot", "token_indices_sorted_by_slot", "active_slot_ids", "num_tokens_per_slot", "slot_start_offsets"):
+        assert torch.equal(getattr(mine, name), getattr(host, name)), f"graph buffers: {name} differs"
+    # --- vLLM-style kernel metadata
+    km_host = LoRAKernelMeta.make(S, T, DEV)
+    km_host.prepare_tensors(dev)
+    km_dev = LoRAKernelMeta.make(S, T, DEV)
+    km_dev.token_indices_sorted_by_lora_ids.copy_(km_host.token_indices_sorted_by_lora_ids)  # same uninitialised tail
+    km_dev.token_lora_mapping.copy_(km_host.token_lora_mapping)
+    km_dev.active_lora_ids.fill_(7)
+    km_dev.num_tokens_per_lora.fill_(7)
+    km_dev.lora_token_start_loc.fill_(7)
+    km_dev.prepare_tensors_on_device(dev)
+    torch.cuda.synchronize()
+    for name in ("token_indices_sorted_by_lora_ids", "active_lora_ids", "num_tokens_per_lora", "lora_token_start_loc"):
+        a, b = getattr(km_dev, name), getattr(km_host, name)
+        if name == "token_indices_sorted_by_lora_ids" and p_none == 1.0:
+            continue  # the host builder returns before it writes the order
+        assert torch.equal(a, b), f"kernel meta: {name} differs"
+    # --- eager plan (compact, no -1 bucket)
+    plan = BP.build_lora_batch_plan_from_token_to_slot({}, slots.tolist())
+    srt = torch.full((T,), -5, dtype=torch.int32, device=DEV)
+    ids = torch.empty(S + 1, dtype=torch.int32, device=DEV)
+    cnt = torch.empty(S + 1, dtype=torch.int32, device=DEV)
+    off = torch.empty(S + 2, dtype=torch.int32, device=DEV)
+    info = torch.zeros(3, dtype=torch.int32, device=DEV)
+    N.build_metadata(dev, S, N.META_EAGER, srt, ids, cnt, off, info)
+    k, rows, bad = info.tolist()
+    assert (k, rows, bad) == (len(plan.active_slot_ids), len(plan.token_indices_sorted_by_slot), 0)
+    assert srt[:rows].tolist() == list(plan.token_indices_sorted_by_slot) and bool((srt[rows:] == -5).all())
+    assert ids[:k].tolist() == list(plan.active_slot_ids) and bool((ids[k:] == -1).all())
+    assert cnt[:k].tolist() == list(plan.num_tokens_per_slot) and bool((cnt[k:] == 0).all())
+    assert off[: k + 1].tolist() == list(plan.slot_start_offsets) and bool((off[k + 1:] == 0).all())
+
+
+def test_device_metadata_feeds_the_decode_kernel_and_reports_bad_ids():
+    p = W.decode_projection("qkv", seed=21)
+    d = p.to_device(DEV)
+    bufs = BP.GraphLoRABuffers.make(256, 32, device=DEV)
+    bufs.load_token_to_slot_on_device(d.token_to_slot)
+    ctx = bufs.context(256)
+    meta = LORA.LoRAMetadata(ctx.token_to_slot, ctx.token_indices_sorted_by_slot, ctx.active_slot_ids,
+                             ctx.num_tokens_per_slot, ctx.slot_start_offsets, False, ctx.num_active_loras)
+    y = d.y.clone()
+    LORA.launch_add(y, d.x, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets, meta, 1.0, impl=N.IMPL_BGMV)
+    torch.cuda.synchronize()
+    check_against_oracle(p, y.cpu(), p.y, what="decode kernel on device-built graph buffers")
+    # ids outside [-1, S) are counted and treated as "no adapter"
+    bad = torch.tensor([0, 1, 9, -3, 1, -1], dtype=torch.int32, device=DEV)
+    srt = torch.empty(6, dtype=torch.int32, device=DEV)
+    cnt = torch.empty(3, dtype=torch.int32, device=DEV)
+    off = torch.empty(4, dtype=torch.int32, device=DEV)
+    info = torch.zeros(3, dtype=torch.int32, device=DEV)
+    N.build_metadata(bad, 2, N.META_GRAPH, srt, None, cnt, off, info)
+    assert info.tolist() == [3, 3, 2] and cnt.tolist() == [0, 1, 2] and off.tolist() == [0, 0, 1, 3] and srt[:3].tolist() == [0, 1, 4]
+    with pytest.raises(RuntimeError, match="metadata build"):
+        N.build_metadata(torch.zeros(20000, dtype=torch.int32, device=DEV), 2, N.META_GRAPH,
+                         torch.empty(20000, dtype=torch.int32, device=DEV), None, cnt, off, None)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        N.build_metadata(torch.zeros(4, dtype=torch.int32), 2, N.META_GRAPH, srt, None, cnt, off, None)
