@@ -61,14 +61,26 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "linear"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "linear", "backbone"],
                     help="decode = the headline decode BGMV layer; prefill = prefill SGMV add (tcgen05 kernels) of one "
-                         "layer; linear = base GEMM + LoRA in one tensor-core kernel for the same layer")
+                         "layer; linear = base GEMM + LoRA in one tensor-core kernel for the same layer; backbone = whole "
+                         "decoder steps (prefill + graph-replayed decode) around the LoRA linears")
     ap.add_argument("--only", default=None, choices=["qkv", "o", "gate_up", "down"],
                     help="tuning: time one projection of every layer instead of all four")
     ap.add_argument("--option", action="append", default=[], metavar="KEY=VALUE",
                     help="tuning: lora_b200_set_option before the run (cluster, pdl, ring_kb, decode_kernel, smem_kb)")
     return ap.parse_args()
+
+
+def apply_options(args):
+    """--option key=value -> lora_b200_set_option (tuning runs and the ncu commands in profiles/)."""
+    from nanovllm_voxcpm_b200 import _native as N
+
+    keys = {"cluster": N.OPT_CLUSTER, "pdl": N.OPT_PDL, "ring_kb": N.OPT_RING_KB,
+            "decode_kernel": N.OPT_DECODE_KERNEL, "smem_kb": N.OPT_SMEM_KB}
+    for item in args.option:
+        key, _, value = item.partition("=")
+        N.set_option(keys[key], int(value))
 
 
 def measured_peak():
@@ -255,11 +267,7 @@ def run_gpu_arm(args):
     if not status.available:
         raise RuntimeError(f"B200 LoRA backend unavailable: {status.reason}")
 
-    option_keys = {"cluster": N.OPT_CLUSTER, "pdl": N.OPT_PDL, "ring_kb": N.OPT_RING_KB,
-                   "decode_kernel": N.OPT_DECODE_KERNEL, "smem_kb": N.OPT_SMEM_KB}
-    for item in args.option:
-        key, _, value = item.partition("=")
-        N.set_option(option_keys[key], int(value))
+    apply_options(args)
     slots, work = build_gpu_workload(device, args.layers)
     if args.only:
         work = [[p for p in layer if p["name"] == args.only] for layer in work]
@@ -626,8 +634,77 @@ def run_reference_gpu_arm(args):
     }))
 
 
+# ------------------------------------------------------------------ whole decoder step around the LoRA linears
+def run_backbone_arm(args):
+    """Random-init 24-layer decoder (hidden 1024, 16 q / 2 kv heads x 64, intermediate 4096), 64 requests with
+    prompts of 128-512 tokens, 128 resident rank-32 adapters (4.3 GB of slabs), adapter per request ~ Zipf(1.1):
+    one prefill pass over all prompts, then decode steps of one token per request replayed from a CUDA graph.
+    Attention / norms / RoPE / activation are library code (flash_attn, torch); timed with and without adapters."""
+    from nanovllm_voxcpm_b200 import _native as N
+    from nanovllm_voxcpm_b200 import backbone as BB
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise RuntimeError("--workload backbone is a single-GPU measurement")
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    apply_options(args)
+    cfg = BB.DecoderConfig(num_layers=args.layers)
+    n_req, decode_steps = 64, args.steps if args.steps != 20 else 512
+    gen = torch.Generator().manual_seed(0)
+    prompts = torch.randint(128, 513, (n_req,), generator=gen).tolist()
+    work = BB.BackboneWorkload(prompts, BB.zipf_adapters(n_req, cfg.max_loras, 1.1, seed=0), decode_steps)
+    with torch.device(device):
+        model = BB.Decoder(cfg).to(torch.bfloat16)
+    model.init_random_(0)
+    model.fill_adapter_slots_(cfg.max_loras, cfg.max_lora_rank, seed=1)
+    backend_name = "B200LoRABackend"
+    if args.impl == "reference-gpu":
+        # same decoder, same layers, but every LoRA call goes to the unmodified reference's own GPU backend
+        try:
+            sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+            import nanovllm_voxcpm.lora as RL
+            from nanovllm_voxcpm_b200 import lora as LORA
+
+            status = RL.get_availability()
+            if not status.available:
+                raise RuntimeError(f"reference backend unavailable: {status.reason}")
+            LORA.set_backend_for_testing(RL.get_backend())
+            backend_name = type(RL.get_backend()).__name__
+        except Exception as exc:
+            print(json.dumps({"impl": "reference-gpu", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}))
+            return
+    result = {}
+    for tag, use_lora in (("lora", True), ("base", False)):
+        runner = BB.BackboneRunner(model, work, use_lora=use_lora)
+        runner.prefill()  # warm-up (cuBLAS / flash_attn set-up, scratch allocation)
+        p_tok, p_ms = runner.prefill()
+        d_tok, d_ms, mode = runner.decode(decode_steps, use_graph=not args.no_graph)
+        result[tag] = {"prefill_tokens_per_s": p_tok / (p_ms * 1e-3), "prefill_ms": p_ms, "prefill_tokens": p_tok,
+                       "decode_tokens_per_s": d_tok / (d_ms * 1e-3), "decode_ms_per_step": d_ms / decode_steps,
+                       "launch_mode": mode}
+    lora, base = result["lora"], result["base"]
+    print(json.dumps({
+        "metric": "decoder backbone decode tokens/s with 128 resident adapters (64 requests x 1 token per step)",
+        "value": lora["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": decode_steps, "warmup": 3,
+        "ms_per_step": lora["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"decoder backbone: {cfg.num_layers} layers, hidden 1024, 16/2 heads x 64, intermediate 4096, "
+                               f"{n_req} requests, prompts 128-512 (sum {sum(prompts)}), {decode_steps} decode steps, "
+                               f"{cfg.max_loras} adapters rank {cfg.max_lora_rank}, Zipf(1.1) "
+                               f"({len(set(work.adapter_of_request))} distinct in the batch), paged KV block 256"},
+        "with_adapters": lora, "without_adapters": base,
+        "adapter_overhead": {"decode": base["decode_tokens_per_s"] / lora["decode_tokens_per_s"],
+                             "prefill": base["prefill_tokens_per_s"] / lora["prefill_tokens_per_s"]},
+        "device_status": N.device_status(), "impl": args.impl, "lora_backend": backend_name,
+    }))
+
+
 def main():
     args = parse_args()
+    if args.workload == "backbone" and args.impl in ("b200", "reference-gpu"):
+        return run_backbone_arm(args)
     if args.impl == "reference":
         run_reference_arm(args)
     elif args.impl == "reference-gpu":

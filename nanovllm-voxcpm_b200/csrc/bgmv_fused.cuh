@@ -544,7 +544,9 @@ inline bool bgmv_plan(const BgmvProblem& b, BgmvParams* pp, const char** why) {
   const int Q = st.n * b.r_max;
   int C = bgmv_options().cluster;
   if (C != 1 && C != 2 && C != 4 && C != 8) {
-    C = b.n_buckets <= 37 ? 4 : (b.n_buckets <= 74 ? 2 : 1);
+    // buckets that can hold tokens: graph buffers carry one bucket per slot, most of them empty
+    const int busy = std::min(b.n_buckets, std::max(b.T, 1));
+    C = busy <= 37 ? 4 : (busy <= 74 ? 2 : 1);
   }
   while (C < 8 && round_up_i(ceil_div_i(Q, C), 8) > kBgmvMaxRc) C *= 2;
   const int Rc = round_up_i(ceil_div_i(Q, C), 8);

@@ -545,7 +545,10 @@ inline bool bgmv_split_plan(const BgmvProblem& b, BgmvSplitParams* pp, const cha
 
   const int Q = st.n * b.r_max;
   int C0 = bgmv_options().cluster;
-  if (C0 != 1 && C0 != 2 && C0 != 4 && C0 != 8) C0 = b.n_buckets <= 37 ? 4 : (b.n_buckets <= 74 ? 2 : 1);
+  if (C0 != 1 && C0 != 2 && C0 != 4 && C0 != 8) {
+    const int busy = std::min(b.n_buckets, std::max(b.T, 1));  // buckets that can hold tokens
+    C0 = busy <= 37 ? 4 : (busy <= 74 ? 2 : 1);
+  }
   const int cap0 = std::min(kBgmvSmemMax, (bgmv_split_options().smem_kb > 0 ? bgmv_split_options().smem_kb
                                                                            : kSplitDefaultSmemKb) * 1024);
   BgmvSplitParams p;

@@ -1,0 +1,68 @@
+"""The decoder-step harness around the LoRA linears: the kernels inside a real layer stack
+(prefill through the tensor-core path, decode through the fused kernel, eager and graph replay)
+against the same stack with the CPU-oracle formula as LoRA backend."""
+
+import pytest
+import torch
+
+from helpers import OracleBackend
+from nanovllm_voxcpm_b200 import _native as N
+from nanovllm_voxcpm_b200 import backbone as BB
+from nanovllm_voxcpm_b200 import context as CTX
+from nanovllm_voxcpm_b200 import lora as LORA
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _clean():
+    LORA.set_backend_for_testing(None)
+    CTX.reset_lora_context()
+    yield
+    LORA.set_backend_for_testing(None)
+    CTX.reset_lora_context()
+    assert N.device_status() == 0
+
+
+def _model_and_work():
+    pytest.importorskip("flash_attn")
+    cfg = BB.DecoderConfig(hidden_size=256, num_heads=4, num_kv_heads=2, head_dim=64, intermediate_size=512,
+                           num_layers=2, max_loras=8, max_lora_rank=32, max_position=1024)
+    with torch.device("cuda"):
+        model = BB.Decoder(cfg).to(torch.bfloat16)
+    model.init_random_(0, std=0.05)
+    model.fill_adapter_slots_(8, 32, seed=1, std=0.05)
+    # 600 prompt rows: the prefill batch takes the tcgen05 kernels (>= 512 rows), with a request without adapter
+    work = BB.BackboneWorkload([200, 17, 264, 5, 114], [0, 3, -1, 3, 7], decode_steps=3)
+    return model, work
+
+
+def test_backbone_prefill_and_decode_match_the_oracle_backend():
+    model, work = _model_and_work()
+    mine = BB.BackboneRunner(model, work, use_lora=True)
+    mine.prefill()
+    out_prefill = mine.last_output.float().cpu()
+    mine.decode(3, use_graph=True)
+    out_graph = mine.last_output.float().cpu()
+
+    eager = BB.BackboneRunner(model, work, use_lora=True)
+    eager.prefill()
+    eager.decode(3, use_graph=False)
+    assert torch.equal(out_graph, eager.last_output.float().cpu()), "graph replay and eager launches differ"
+
+    base = BB.BackboneRunner(model, work, use_lora=False)
+    base.prefill()
+    out_base = base.last_output.float().cpu()
+    assert not torch.allclose(out_prefill, out_base, atol=1e-3), "adapters changed nothing"
+
+    LORA.set_backend_for_testing(OracleBackend())
+    ref = BB.BackboneRunner(model, work, use_lora=True)
+    ref.prefill()
+    ref_prefill = ref.last_output.float().cpu()
+    ref.decode(3, use_graph=False)
+    ref_decode = ref.last_output.float().cpu()
+    # two bf16 layers around the op: tolerance of the stack, not of the kernel
+    torch.testing.assert_close(out_prefill, ref_prefill, atol=6e-2, rtol=6e-2)
+    torch.testing.assert_close(out_graph, ref_decode, atol=6e-2, rtol=6e-2)
+    # the request without adapter sees exactly the base model in prefill (rows 217..480 of the single chunk)
+    assert torch.equal(out_prefill[217:481], out_base[217:481])
