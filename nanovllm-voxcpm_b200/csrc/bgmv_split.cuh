@@ -118,7 +118,7 @@ bgmv_split_kernel(const __grid_constant__ BgmvSplitParams p, const __grid_consta
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_bar);  // full[], empty[], part_ready, recv_free
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kSplitMaxStages + 2);
-  int* tab = reinterpret_cast<int*>(smem + p.off_bar + 256);       // e_lo[4], e_n[4], e_tiles[4]
+  int* tab = reinterpret_cast<int*>(smem + p.off_bar + 256);       // e_lo[4], e_n[4], e_tiles[4], first y column[4]
   const uint32_t bar_base = smem_u32(bars);
   const uint32_t ring_base = smem_u32(smem);
   const uint32_t part_ready = bar_base + 8u * (uint32_t)(2 * kSplitMaxStages);
@@ -145,6 +145,7 @@ bgmv_split_kernel(const __grid_constant__ BgmvSplitParams p, const __grid_consta
     tab[s] = lo;
     tab[4 + s] = en;
     tab[8 + s] = (en + ER - 1) >> p.er_shift;
+    tab[12 + s] = (s < n ? p.st.col[s] : 0) + lo;  // first y column of this CTA's rows of slice s
   }
   if (tid == kSplitConsumers)
     for (int s = 0; s < n; ++s) tma_prefetch_desc(&maps.a[s]);
@@ -173,11 +174,12 @@ bgmv_split_kernel(const __grid_constant__ BgmvSplitParams p, const __grid_consta
   // barriers. Consumers wait on it before their first remote store, the producer before it exits.
   cluster_arrive();
 
+  const int er_shift = p.er_shift;
   // next expand tile of this CTA in (slice, tile) order; the caller knows one is left
   auto next_tile = [&](int& cs, int& cet, int& s_out, int& r0_out) {
     while (cs < B200_LORA_MAX_SLICES - 1 && cet >= tab[8 + cs]) { ++cs; cet = 0; }
     s_out = cs;
-    r0_out = cet << p.er_shift;
+    r0_out = cet << er_shift;
     ++cet;
   };
 
@@ -252,46 +254,64 @@ bgmv_split_kernel(const __grid_constant__ BgmvSplitParams p, const __grid_consta
       }
     }
   }
-  cluster_wait();  // start-up barrier: peers run and their barriers are initialised
-  if (p.use_pdl) griddep_wait();  // x and y of this launch are final from here on
-  B200_TRACE_POINT(4)
-
+  // Launch parameters live in constant memory that is cold for every new launch: whatever the code
+  // after the wait needs is read here and pinned in registers, so that no constant-cache miss sits
+  // on the critical path.
+  uint32_t xs_base = smem_u32(smem + p.off_x), ys_base = smem_u32(smem + p.off_y);
+  uint32_t recv_base = smem_u32(smem + p.off_recv), tmp_base = smem_u32(smem + p.off_tmp);
+  uint32_t pitchB = (uint32_t)p.r_max * 2u, pitchA = (uint32_t)BC * 2u;
+  uint32_t pitchX = (uint32_t)p.pitchX, pitchT = (uint32_t)p.pitchT, stage_bytes = (uint32_t)p.stage_bytes;
+  int pitchP = p.pitchP, kblocks = r_eff >> 5, t_rows = p.T;
+  const __nv_bfloat16* x_ptr = p.x;
+  __nv_bfloat16* y_ptr = p.y;
+  int64_t x_ld = p.x_ld, y_ld = p.y_ld;
+  const int32_t* sorted_ptr = p.sorted_idx;
+  asm volatile("" : "+r"(xs_base), "+r"(ys_base), "+r"(recv_base), "+r"(tmp_base), "+r"(pitchB), "+r"(pitchA));
+  asm volatile("" : "+r"(pitchX), "+r"(pitchT), "+r"(stage_bytes), "+r"(pitchP), "+r"(kblocks), "+r"(t_rows));
+  asm volatile("" : "+l"(x_ptr), "+l"(y_ptr), "+l"(x_ld), "+l"(y_ld), "+l"(sorted_ptr));
   int c_stage = 0, c_round = 0;
   auto advance = [&]() {
     if (++c_stage == NS) { c_stage = 0; ++c_round; }
   };
-  const uint32_t xs_base = smem_u32(smem + p.off_x);
-  const uint32_t ys_base = smem_u32(smem + p.off_y);
-  const uint32_t recv_base = smem_u32(smem + p.off_recv);
-  const uint32_t tmp_base = smem_u32(smem + p.off_tmp);
-  const uint32_t pitchB = (uint32_t)p.r_max * 2u;
-  const uint32_t pitchA = (uint32_t)BC * 2u;
-  const int kblocks = r_eff >> 5;
+  cluster_wait();  // start-up barrier: peers run and their barriers are initialised
+  if (p.use_pdl) griddep_wait();  // x and y of this launch are final from here on
+  B200_TRACE_POINT(4)
 
   for (int pass = 0; pass < npass; ++pass) {
     int tok_lo = tok0_lo, tok_hi = tok0_hi;
     if (pass > 0) {
       tok_lo = tok_hi = -1;
-      if (pass * 16 + g < cnt) tok_lo = p.sorted_idx[start + pass * 16 + g];
-      if (pass * 16 + g + 8 < cnt) tok_hi = p.sorted_idx[start + pass * 16 + g + 8];
-      if (tok_lo >= p.T) tok_lo = -1;
-      if (tok_hi >= p.T) tok_hi = -1;
+      if (pass * 16 + g < cnt) tok_lo = sorted_ptr[start + pass * 16 + g];
+      if (pass * 16 + g + 8 < cnt) tok_hi = sorted_ptr[start + pass * 16 + g + 8];
+      if (tok_lo >= t_rows) tok_lo = -1;
+      if (tok_hi >= t_rows) tok_hi = -1;
       if (tid == 0) mbar_arrive_expect_tx(part_ready, (uint32_t)(C * 16 * Qeff * 4));
     }
 
     // ---- stage x[16 tokens, Kc] (warp w copies token rows 4w..4w+3); absent rows / columns are zero.
     // Row r's token index sits in lane 4*(r%8) of this warp (tok_lo for r < 8, tok_hi above).
+    // (plain loads into registers, then shared-memory stores: their issue does not serialise the way
+    //  16-byte cp.async copies of rows nobody on this SM has touched do)
+    int row_tok[4];  // the shuffles run with all 32 lanes, outside the lane-dependent column loop
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int r = warp * 4 + i;
-      const int tok = __shfl_sync(0xffffffffu, r < 8 ? tok_lo : tok_hi, (r & 7) * 4);
-      const uint32_t row = xs_base + (uint32_t)r * (uint32_t)p.pitchX;
-      for (int k8 = lane * 8; k8 < Kc; k8 += 256) {
-        if (tok >= 0 && k_lo + k8 < in_dim) cp_async16(row + (uint32_t)k8 * 2u, p.x + (int64_t)tok * p.x_ld + k_lo + k8);
-        else sts128_zero(row + (uint32_t)k8 * 2u);
+      row_tok[i] = __shfl_sync(0xffffffffu, r < 8 ? tok_lo : tok_hi, (r & 7) * 4);
+    }
+    for (int k8 = lane * 8; k8 < Kc; k8 += 256) {
+      uint4 xv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        xv[i] = make_uint4(0, 0, 0, 0);
+        if (row_tok[i] >= 0 && k_lo + k8 < in_dim) xv[i] = ldg128(x_ptr + (int64_t)row_tok[i] * x_ld + k_lo + k8);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t dst = xs_base + (uint32_t)(warp * 4 + i) * pitchX + (uint32_t)k8 * 2u;
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(xv[i].x), "r"(xv[i].y), "r"(xv[i].z), "r"(xv[i].w) : "memory");
       }
     }
-    cp_async_commit();
+    cp_async_commit();  // (empty group: keeps the group count of the y slots below)
     if (pass == 0) { B200_TRACE_POINT(24) }
 
     // ---- request y of the first expand tiles (per-thread staging slots)
@@ -302,14 +322,14 @@ bgmv_split_kernel(const __grid_constant__ BgmvSplitParams p, const __grid_consta
         int s, r0;
         next_tile(ycs, yet, s, r0);
         const int nrows = min(ER, tab[4 + s] - r0);
-        const int col = p.st.col[s] + tab[s] + r0;
+        const int col = tab[12 + s] + r0;
 #pragma unroll
         for (int bi = 0; bi < 2; ++bi) {
           const int rb = (warp + kSplitWarps * bi) * 32;
           if (rb + 8 * t < nrows) {
             const uint32_t dst = ys_base + (uint32_t)((((d * 2 + bi) * 2) * kSplitConsumers + tid) * 16);
-            if (tok_lo >= 0) cp_async16(dst, p.y + (int64_t)tok_lo * p.y_ld + col + rb + 8 * t);
-            if (tok_hi >= 0) cp_async16(dst + kSplitConsumers * 16, p.y + (int64_t)tok_hi * p.y_ld + col + rb + 8 * t);
+            if (tok_lo >= 0) cp_async16(dst, y_ptr + (int64_t)tok_lo * y_ld + col + rb + 8 * t);
+            if (tok_hi >= 0) cp_async16(dst + kSplitConsumers * 16, y_ptr + (int64_t)tok_hi * y_ld + col + rb + 8 * t);
           }
         }
       }
@@ -327,13 +347,13 @@ bgmv_split_kernel(const __grid_constant__ BgmvSplitParams p, const __grid_consta
     if (pass > 0) mbar_wait_bounded_acquire_cluster(recv_free, (uint32_t)((pass - 1) & 1), abort_flag);
 
     // ===== shrink: partial[16 tok, 8 rows of this warp] over this CTA's columns, per 32-row box =====
-    const uint32_t xlo_base = xs_base + (uint32_t)g * (uint32_t)p.pitchX + (uint32_t)t * 16u;
-    const uint32_t xhi_base = xlo_base + 8u * (uint32_t)p.pitchX;
+    const uint32_t xlo_base = xs_base + (uint32_t)g * pitchX + (uint32_t)t * 16u;
+    const uint32_t xhi_base = xlo_base + 8u * pitchX;
     // (tok g | g+8, stacked rows q, q+1) of this CTA's column range -> every CTA of the cluster
     auto send = [&](int grp, const float (&a)[4], const float (&b)[4]) {
       const int q = grp * 32 + 8 * warp + 2 * t;  // boxes are stacked in (slice, row box) order
-      const uint32_t dlo = recv_base + (uint32_t)(((c * 16 + g) * p.pitchP + q) * 4);
-      const uint32_t dhi = dlo + (uint32_t)(8 * p.pitchP * 4);
+      const uint32_t dlo = recv_base + (uint32_t)(((c * 16 + g) * pitchP + q) * 4);
+      const uint32_t dhi = dlo + (uint32_t)(8 * pitchP * 4);
       for (int rc = 0; rc < C; ++rc) {
         const uint32_t rbar = mapa_shared(part_ready, (uint32_t)rc);
         st_async_f32x2(mapa_shared(dlo, (uint32_t)rc), a[0] + b[0], a[1] + b[1], rbar);
@@ -362,7 +382,7 @@ bgmv_split_kernel(const __grid_constant__ BgmvSplitParams p, const __grid_consta
         for (int grp = 0; grp < kSplitMaxGroups; ++grp) {
           if (grp < G) {
             mbar_wait_bounded(full_bar(c_stage), (uint32_t)(c_round & 1), abort_flag);
-            const uint32_t wbase = ring_base + (uint32_t)c_stage * (uint32_t)p.stage_bytes +
+            const uint32_t wbase = ring_base + (uint32_t)c_stage * stage_bytes +
                                    (uint32_t)(8 * warp + g) * pitchA + (uint32_t)t * 16u;
             uint4 w[kSplitBoxCols / 32];
 #pragma unroll
@@ -396,11 +416,11 @@ bgmv_split_kernel(const __grid_constant__ BgmvSplitParams p, const __grid_consta
 #pragma unroll
         for (int rc = 0; rc < 8; ++rc) {
           v[rc] = make_float2(0.f, 0.f);
-          if (rc < C) v[rc] = lds_f32x2(recv_base + (uint32_t)(((rc * 16 + tok) * p.pitchP + 2 * pr) * 4));
+          if (rc < C) v[rc] = lds_f32x2(recv_base + (uint32_t)(((rc * 16 + tok) * pitchP + 2 * pr) * 4));
         }
         const float s0 = ((v[0].x + v[1].x) + (v[2].x + v[3].x)) + ((v[4].x + v[5].x) + (v[6].x + v[7].x));
         const float s1 = ((v[0].y + v[1].y) + (v[2].y + v[3].y)) + ((v[4].y + v[5].y) + (v[6].y + v[7].y));
-        sts32(tmp_base + (uint32_t)tok * (uint32_t)p.pitchT + (uint32_t)pr * 4u, pack_bf16x2(s0 * sc, s1 * sc));
+        sts32(tmp_base + (uint32_t)tok * pitchT + (uint32_t)pr * 4u, pack_bf16x2(s0 * sc, s1 * sc));
       }
     }
     if (pass == 0) { B200_TRACE_POINT(28) }
@@ -409,18 +429,18 @@ bgmv_split_kernel(const __grid_constant__ BgmvSplitParams p, const __grid_consta
     if (pass == 0) { B200_TRACE_POINT(8) }
 
     // ===== expand: y[tok, cols] += tmp[16 tok, r] . B_rows^T =====
-    const uint32_t tmp_lo = tmp_base + (uint32_t)g * (uint32_t)p.pitchT + (uint32_t)t * 16u;
-    const uint32_t tmp_hi = tmp_lo + 8u * (uint32_t)p.pitchT;
+    const uint32_t tmp_lo = tmp_base + (uint32_t)g * pitchT + (uint32_t)t * 16u;
+    const uint32_t tmp_hi = tmp_lo + 8u * pitchT;
     int ccs = 0, cet = 0;
     for (int e = 0; e < tiles_exp; ++e) {
       int s_cur, r0;
       next_tile(ccs, cet, s_cur, r0);
       const int nrows = min(ER, tab[4 + s_cur] - r0);
-      const int col = p.st.col[s_cur] + tab[s_cur] + r0;
+      const int col = tab[12 + s_cur] + r0;
       const int d_slot = e % kSplitYDepth;
       mbar_wait_bounded(full_bar(c_stage), (uint32_t)(c_round & 1), abort_flag);
-      if (pass == 0 && e < 3) { B200_TRACE_POINT(12 + 4 * e) }
-      const uint32_t sbase = ring_base + (uint32_t)c_stage * (uint32_t)p.stage_bytes;
+      if (pass == 0 && e < 1) { B200_TRACE_POINT(12 + 4 * e) }
+      const uint32_t sbase = ring_base + (uint32_t)c_stage * stage_bytes;
       // this warp's (up to) two 32-row blocks of the tile, interleaved: 8 independent accumulators
       float d[2][4][4];
 #pragma unroll
@@ -456,7 +476,7 @@ bgmv_split_kernel(const __grid_constant__ BgmvSplitParams p, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(c_stage));  // the tile is in registers now
       advance();
-      if (pass == 0 && e < 3) { B200_TRACE_POINT(13 + 4 * e) }
+      if (pass == 0 && e < 1) { B200_TRACE_POINT(13 + 4 * e) }
       cp_async_wait<kSplitYDepth - 1>();  // y of tile e (this thread's own copies) is in its slot
 #pragma unroll
       for (int bi = 0; bi < 2; ++bi) {
@@ -470,7 +490,7 @@ bgmv_split_kernel(const __grid_constant__ BgmvSplitParams p, const __grid_consta
             v.y = add_bf16x2(v.y, d[bi][1][0], d[bi][1][1]);
             v.z = add_bf16x2(v.z, d[bi][2][0], d[bi][2][1]);
             v.w = add_bf16x2(v.w, d[bi][3][0], d[bi][3][1]);
-            stg128(p.y + (int64_t)tok_lo * p.y_ld + cc, v);
+            stg128(y_ptr + (int64_t)tok_lo * y_ld + cc, v);
           }
           if (tok_hi >= 0) {
             uint4 v = lds128(src + kSplitConsumers * 16);
@@ -478,12 +498,12 @@ bgmv_split_kernel(const __grid_constant__ BgmvSplitParams p, const __grid_consta
             v.y = add_bf16x2(v.y, d[bi][1][2], d[bi][1][3]);
             v.z = add_bf16x2(v.z, d[bi][2][2], d[bi][2][3]);
             v.w = add_bf16x2(v.w, d[bi][3][2], d[bi][3][3]);
-            stg128(p.y + (int64_t)tok_hi * p.y_ld + cc, v);
+            stg128(y_ptr + (int64_t)tok_hi * y_ld + cc, v);
           }
         }
       }
       y_issue(d_slot);  // the slot is free again: request tile e + depth into it
-      if (pass == 0 && e < 3) { B200_TRACE_POINT(14 + 4 * e) }
+      if (pass == 0 && e < 1) { B200_TRACE_POINT(14 + 4 * e) }
     }
     cp_async_wait<0>();
     if (pass == 0) { B200_TRACE_POINT(10) }

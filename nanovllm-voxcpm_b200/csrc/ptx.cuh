@@ -64,7 +64,10 @@ __device__ __forceinline__ bool mbar_try_wait_acquire_cluster(uint32_t bar, uint
 // returns at once, so control flow never depends on a barrier that cannot
 // complete. Returns false when it gave up.
 constexpr int kSpinLimit = 1 << 22;
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// The polling loops live out of line: a wait whose barrier has already completed (the common case
+// once the weights are resident) costs one try_wait at the call site, and the kernels' code stays
+// small enough for the instruction cache.
+__device__ __noinline__ bool mbar_spin_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   for (int it = 0; it < kSpinLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag != 0) return false;
@@ -72,14 +75,22 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   *abort_flag = 1;
   return false;
 }
-__device__ __forceinline__ bool mbar_wait_bounded_acquire_cluster(uint32_t bar, uint32_t parity,
-                                                                  volatile int* abort_flag) {
+__device__ __noinline__ bool mbar_spin_bounded_acquire_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   for (int it = 0; it < kSpinLimit; ++it) {
     if (mbar_try_wait_acquire_cluster(bar, parity)) return true;
     if (*abort_flag != 0) return false;
   }
   *abort_flag = 1;
   return false;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_spin_bounded(bar, parity, abort_flag);
+}
+__device__ __forceinline__ bool mbar_wait_bounded_acquire_cluster(uint32_t bar, uint32_t parity,
+                                                                  volatile int* abort_flag) {
+  if (mbar_try_wait_acquire_cluster(bar, parity)) return true;
+  return mbar_spin_bounded_acquire_cluster(bar, parity, abort_flag);
 }
 
 // ---------------------------------------------------- bulk async copy (1-D)
