@@ -13,8 +13,9 @@ in L2 from the previous step (126 MB L2): inputs larger than L2 is the cache-def
              write for rows with an adapter) with everything resident in HBM; the step is
              replayed as one CUDA graph and timed with CUDA events.
   e2e        the same metric through the public backend call (`B200LoRABackend.add_lora`)
-             with host buffers: every call copies x and y from pinned host memory and reads
-             y back, all inside the timed region.
+             with host buffers: every layer's x and y come from pinned host memory (one packed
+             copy per layer) and its y goes back to the host, all inside the timed region;
+             copies and launches are pipelined over three streams.
   roofline   HBM roofline of the dominant kernel (bgmv_fused_kernel): algorithmic bytes per
              launch / average launch duration, against the measured copy bandwidth.
   cpu_baseline / --impl reference
@@ -339,22 +340,54 @@ def run_gpu_arm(args):
     # ---- e2e: public backend call with host buffers ---------------------------------
     e2e = None
     if not args.no_e2e:
-        host = []
-        for p in work[0]:
-            host.append(dict(x=p["x"].cpu().pin_memory(), y=p["y"].cpu().pin_memory(),
-                             out=torch.empty_like(p["y"], device="cpu").pin_memory()))
-        h2d = sum(h["x"].numel() * 2 + h["y"].numel() * 2 for h in host) * args.layers
-        d2h = sum(h["out"].numel() * 2 for h in host) * args.layers
+        # Host side of a step: per layer ONE pinned staging buffer holding x and y of its projections
+        # (x block first, then the y block), mirrored by one device buffer whose slices the LoRA calls
+        # use; a layer costs one host->device copy (x and y) and one device->host copy (the y block).
+        def packed_layer(layer):
+            nx = sum(p["x"].numel() for p in layer)
+            ny = sum(p["y"].numel() for p in layer)
+            dev = torch.empty(nx + ny, dtype=torch.bfloat16, device=device)
+            hst = torch.empty(nx + ny, dtype=torch.bfloat16).pin_memory()
+            out = torch.empty(ny, dtype=torch.bfloat16).pin_memory()
+            views, ox, oy = [], 0, nx
+            for p in layer:
+                xv = dev[ox: ox + p["x"].numel()].view_as(p["x"])
+                yv = dev[oy: oy + p["y"].numel()].view_as(p["y"])
+                hst[ox: ox + p["x"].numel()].copy_(p["x"].flatten().cpu())
+                hst[oy: oy + p["y"].numel()].copy_(p["y"].flatten().cpu())
+                views.append(dict(x=xv, y=yv, ys=list(yv.split(p["outs"], dim=-1)), a=p["a"], b=p["b"]))
+                ox += p["x"].numel()
+                oy += p["y"].numel()
+            return dict(dev=dev, host=hst, out=out, nx=nx, views=views)
+
+        packed = [packed_layer(layer) for layer in work]
+        h2d = sum(pl["host"].numel() * 2 for pl in packed)
+        d2h = sum(pl["out"].numel() * 2 for pl in packed)
         eager_meta = None
+        # Three streams: host->device copies, the LoRA launches, device->host reads, pipelined over the
+        # layers; the next step may overwrite a layer's buffer only after its read-back has finished.
+        s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        ev_in = [torch.cuda.Event() for _ in packed]
+        ev_done = [torch.cuda.Event() for _ in packed]
+        ev_out = [torch.cuda.Event() for _ in packed]
+        for ev in ev_out:
+            ev.record(stream)
 
         def e2e_step():
-            for layer in work:
-                for p, h in zip(layer, host):
-                    p["x"].copy_(h["x"], non_blocking=True)
-                    p["y"].copy_(h["y"], non_blocking=True)
-                    backend.add_lora(list(p["y"].split(p["outs"], dim=-1)), p["x"], p["a"], p["b"],
-                                     indices=meta.token_to_slot, metadata=meta, scaling=1.0, y_packed=p["y"])
-                    h["out"].copy_(p["y"], non_blocking=True)
+            for li, pl in enumerate(packed):
+                with torch.cuda.stream(s_in):
+                    s_in.wait_event(ev_out[li])
+                    pl["dev"].copy_(pl["host"], non_blocking=True)
+                    ev_in[li].record(s_in)
+                stream.wait_event(ev_in[li])
+                for v in pl["views"]:
+                    backend.add_lora(v["ys"], v["x"], v["a"], v["b"], indices=meta.token_to_slot, metadata=meta,
+                                     scaling=1.0, y_packed=v["y"])
+                ev_done[li].record(stream)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_done[li])
+                    pl["out"].copy_(pl["dev"][pl["nx"]:], non_blocking=True)
+                    ev_out[li].record(s_out)
 
         with torch.cuda.stream(stream):
             for _ in range(min(args.warmup, 3)):
@@ -363,8 +396,10 @@ def run_gpu_arm(args):
             s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             n_e2e = max(3, min(args.steps, 10))
             s2.record(stream)
+            s_in.wait_event(s2)
             for _ in range(n_e2e):
                 e2e_step()
+            stream.wait_stream(s_out)  # the last read-back ends the timed region
             e2.record(stream)
             e2.synchronize()
             barrier()
