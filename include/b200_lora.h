@@ -213,6 +213,24 @@ int lora_b200_build_metadata(const int32_t* token_to_slot, int32_t T, int32_t S,
                              int32_t* sorted_idx, int32_t* slot_ids, int32_t* counts, int32_t* offsets,
                              int32_t* info, void* stream);
 
+/*
+ * Tensor-parallel exchange of the row-parallel LoRA intermediate: out[i] = sum over the tp ranks of
+ * partial[i], in ONE kernel over peer memory (each rank pushes its partial into every peer's receive
+ * buffer with plain stores over NVLink, publishes per-chunk flags, waits - bounded - for its peers'
+ * and adds). It stands where the reference has no separate collective: there the partial LoRA delta
+ * rides the [T, out] all-reduce of the base output (nanovllm_voxcpm/layers/lora.py:722-742); summing
+ * the [n, T, r] shrink results instead lets every rank expand only its out/tp columns of lora_B.
+ *  partial, out  device float[count] (may alias); count % 4 == 0, count <= capacity
+ *  peer_buffers  host array of tp device pointers: rank r's symmetric buffer of
+ *                lora_b200_tp_exchange_bytes(tp, capacity) bytes, zero-filled once, mapped into
+ *                this process (CUDA IPC / symmetric memory); entry [rank] is the local one
+ * Every rank must issue the same sequence of calls. The exchange counter lives in the buffer, so
+ * a captured CUDA graph replays correctly. A wait that gives up sets bit 2 of the device status.
+ */
+int lora_b200_tp_allreduce(const float* partial, float* out, int32_t count, void* const* peer_buffers,
+                           int32_t rank, int32_t tp, int32_t capacity, void* stream);
+size_t lora_b200_tp_exchange_bytes(int32_t tp, int32_t capacity);
+
 /* Tuning knobs of the fused decode kernel (process-wide, read at launch time). */
 #define B200_LORA_OPT_CLUSTER 1 /* CTAs per slot bucket: 1, 2, 4, 8; 0 = choose from n_buckets */
 #define B200_LORA_OPT_PDL 2     /* 1 = launch with programmatic stream serialization (default), 0 = off */

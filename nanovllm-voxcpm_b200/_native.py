@@ -64,6 +64,10 @@ _SIGNATURES = {
     "lora_b200_build_metadata": (
         c_int32, [c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     ),
+    "lora_b200_tp_allreduce": (
+        c_int32, [c_void_p, c_void_p, c_int32, POINTER(c_void_p), c_int32, c_int32, c_int32, c_void_p],
+    ),
+    "lora_b200_tp_exchange_bytes": (c_size_t, [c_int32, c_int32]),
     "lora_b200_set_option": (c_int32, [c_int32, c_int32]),
     "lora_b200_device_status": (c_int32, [POINTER(c_int32), c_int32]),
 }

@@ -5,6 +5,7 @@
 #include "bgmv_fused.cuh"
 #include "bgmv_split.cuh"
 #include "metadata.cuh"
+#include "tp_exchange.cuh"
 #include "sgmv_tc.cuh"
 #include "gemm_tc.cuh"
 
@@ -119,6 +120,13 @@ int lora_b200_build_metadata(const int32_t* token_to_slot, int32_t T, int32_t S,
                              int32_t* info, void* stream) {
   return build_metadata(token_to_slot, T, S, convention, sorted_idx, slot_ids, counts, offsets, info,
                         static_cast<cudaStream_t>(stream));
+}
+
+size_t lora_b200_tp_exchange_bytes(int32_t tp, int32_t capacity) { return tp_exchange_bytes(tp, capacity); }
+
+int lora_b200_tp_allreduce(const float* partial, float* out, int32_t count, void* const* peer_buffers, int32_t rank,
+                           int32_t tp, int32_t capacity, void* stream) {
+  return tp_allreduce_launch(partial, out, count, peer_buffers, rank, tp, capacity, static_cast<cudaStream_t>(stream));
 }
 
 #ifdef B200_TRACE

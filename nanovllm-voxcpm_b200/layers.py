@@ -437,6 +437,9 @@ class LoRARowParallelLinear(_LoRALayerBase):
         (``out / r`` times fewer bytes than a second ``[T, out]`` exchange would need),
         after which every rank expands only its ``out / tp`` columns of a ``lora_B`` that
         is sharded on the output dim; the base all-reduce assembles the delta exactly once.
+      * ``"peer_exchange"``: as ``"allreduce_tmp"``, but the ``[T, r]`` sum is one kernel over
+        peer memory (``tp_exchange.TpExchange`` assigned to ``self.tp_exchange``, shared by the
+        layers of a model) instead of a library collective.
     """
 
     def __init__(
@@ -451,12 +454,13 @@ class LoRARowParallelLinear(_LoRALayerBase):
     ):
         rank = max_lora_rank or 0
         super().__init__(max_loras, rank, rank > 0, lora_domain)
-        if lora_tp_mode not in ("partial_y", "allreduce_tmp"):
+        if lora_tp_mode not in ("partial_y", "allreduce_tmp", "peer_exchange"):
             raise ValueError(f"unknown lora_tp_mode {lora_tp_mode!r}")
         self.tp_size, self.tp_rank = _get_world_size(), _get_rank()
         self.input_size, self.output_size = input_size, output_size
         self.shard_input_size = divide(input_size, self.tp_size)
         self.lora_tp_mode = lora_tp_mode if self.tp_size > 1 else "partial_y"
+        self.tp_exchange = None  # TpExchange for "peer_exchange", assigned by whoever builds the model
         self.weight = nn.Parameter(torch.empty(output_size, self.shard_input_size))
         self.bias = nn.Parameter(torch.empty(output_size)) if bias else None
         if self.supports_lora:
@@ -471,7 +475,7 @@ class LoRARowParallelLinear(_LoRALayerBase):
         return [self.lora_B]
 
     def _slice_layout(self):
-        if self.lora_tp_mode == "allreduce_tmp":
+        if self.lora_tp_mode != "partial_y":
             w = self.output_size // self.tp_size
             return [w], [self.tp_rank * w]
         return [self.output_size], [0]
@@ -489,14 +493,19 @@ class LoRARowParallelLinear(_LoRALayerBase):
         y_flat = y if y.dim() == 2 else y.view(-1, y.size(-1))
         tmp = torch.empty((1, x_flat.size(0), self.max_lora_rank), dtype=torch.float32, device=x.device)
         shrink_into(tmp, x_flat, [self.lora_A], token_to_slot, 1.0)
-        dist.all_reduce(tmp)  # [T, r] fp32 partials over the input shards
+        if self.lora_tp_mode == "peer_exchange":
+            if self.tp_exchange is None:
+                raise RuntimeError("lora_tp_mode='peer_exchange' needs a TpExchange in layer.tp_exchange")
+            self.tp_exchange.all_reduce_(tmp)  # one kernel over peer memory
+        else:
+            dist.all_reduce(tmp)  # [T, r] fp32 partials over the input shards
         widths, cols = self._slice_layout()
         expand_into(y_flat, tmp, [self.lora_B], token_to_slot, offset_start=cols[0], add_inputs=True)
         return y
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         bias = self.bias if self.tp_rank == 0 else None
-        if self.lora_tp_mode == "allreduce_tmp":
+        if self.lora_tp_mode != "partial_y":
             y = self._apply_lora_allreduce_tmp(F.linear(x, self.weight, bias), x)
         else:
             y = self._linear(x, self.weight, bias)

@@ -1,0 +1,146 @@
+"""Tensor-parallel LoRA layers on real GPUs: the peer-memory exchange kernel against NCCL and against
+the single-process oracle. The two-rank cases need two GPUs (one process per GPU, NCCL for the
+plumbing, NVLS off, plain peer stores); with one GPU only the single-rank exchange runs."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_exchange_kernel_single_rank_counts_epochs_and_replays_in_a_graph():
+    from nanovllm_voxcpm_b200 import _native as N
+
+    tp, cap = 1, 4096
+    buf = torch.zeros(int(N.lib().lora_b200_tp_exchange_bytes(tp, cap)), dtype=torch.uint8, device="cuda")
+    peers = (N.c_void_p * 1)(buf.data_ptr())
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def exchange(t):
+        N.check(N.lib().lora_b200_tp_allreduce(t.data_ptr(), t.data_ptr(), t.numel(), peers, 0, tp, cap, stream))
+
+    for k, n in enumerate((4096, 8, 1000)):  # different sizes, alternating receive buffers
+        x = torch.randn(n, device="cuda")
+        want = x.clone()
+        exchange(x)
+        torch.cuda.synchronize()
+        assert torch.equal(x, want), f"exchange {k} changed a single-rank sum"
+    state = buf[-64:].view(torch.int32)[:2].tolist()
+    assert state == [3, 0], state
+    # replay: the counter advances on the device, so a captured exchange stays correct
+    x = torch.randn(2048, device="cuda")
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            N.check(N.lib().lora_b200_tp_allreduce(x.data_ptr(), x.data_ptr(), x.numel(), peers, 0, tp, cap, side.cuda_stream))
+        for _ in range(5):
+            g.replay()
+        side.synchronize()
+    assert buf[-64:].view(torch.int32)[0].item() == 8
+    assert N.device_status() == 0
+    with pytest.raises(ValueError, match="multiple of 4"):
+        exchange(torch.zeros(6, device="cuda"))
+
+
+def _worker(rank: int, world: int, port: int, results):
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for p in (root, os.path.join(root, "tests")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=dev)
+    try:
+        from nanovllm_voxcpm_b200 import _native as N
+        from nanovllm_voxcpm_b200 import context as CTX
+        from nanovllm_voxcpm_b200 import layers as L
+        from nanovllm_voxcpm_b200.tp_exchange import TpExchange
+        from oracle import lora_oracle as O
+
+        # ---- the exchange kernel alone: equals the NCCL sum, many rounds, sizes, graph replay
+        ex = TpExchange(capacity=64 * 1024)
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        for n in (4, 4096, 64 * 1024, 1000, 12):
+            for _ in range(3):
+                part = torch.randn(n, device=dev, generator=g)
+                want = part.clone()
+                dist.all_reduce(want)
+                ex.all_reduce_(part)
+                torch.cuda.synchronize()
+                torch.testing.assert_close(part, want, atol=1e-6, rtol=1e-6)
+        part = torch.randn(8192, device=dev, generator=g)
+        keep = part.clone()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                ex.all_reduce_(part)
+            for _ in range(4):
+                part.copy_(keep)
+                graph.replay()
+            side.synchronize()
+        want = keep.clone()
+        dist.all_reduce(want)
+        torch.testing.assert_close(part, want, atol=1e-6, rtol=1e-6)
+
+        # ---- row-parallel layer, three exchange modes, against the single-process oracle
+        gen = torch.Generator().manual_seed(7)  # same tensors on every rank
+        T, hidden, out_f, S, r = 96, 512, 256, 4, 32
+        x = torch.randn(T, hidden, generator=gen).to(torch.bfloat16)
+        w = (torch.randn(out_f, hidden, generator=gen) * 0.05).to(torch.bfloat16)
+        slots = torch.randint(-1, S, (T,), generator=gen, dtype=torch.int32)
+        adapters = {s: ((torch.randn(r, hidden, generator=gen) * 0.1).to(torch.bfloat16),
+                        (torch.randn(out_f, r, generator=gen) * 0.1).to(torch.bfloat16), 1.0 + 0.5 * s) for s in range(S)}
+        a_full, b_full = torch.zeros(S, r, hidden), torch.zeros(S, out_f, r)
+        for s, (a, b, sc) in adapters.items():
+            O.write_slot(a_full, b_full, s, a.float(), b.float(), r, sc)
+        want = O.linear_lora(x, w, None, [a_full.to(torch.bfloat16)], [b_full.to(torch.bfloat16)], [0], slots)
+        CTX.set_lora_context(CTX.build_lora_context_from_token_to_slot(slots.to(dev)))
+        x_shard = x.chunk(world, 1)[rank].contiguous().to(dev)
+        outs = {}
+        for mode in ("partial_y", "allreduce_tmp", "peer_exchange"):
+            layer = L.LoRARowParallelLinear(hidden, out_f, max_loras=S, max_lora_rank=r, lora_tp_mode=mode).to(dev, torch.bfloat16)
+            layer.tp_exchange = ex
+            layer.load_base_shard(w.to(dev))
+            for s, (a, b, sc) in adapters.items():
+                a_shard = a.chunk(world, 1)[rank]
+                b_shard = b if mode == "partial_y" else b.chunk(world, 0)[rank]
+                layer.set_slot_lora(s, a_shard.to(dev), b_shard.to(dev), r, sc)
+            with torch.no_grad():
+                outs[mode] = layer(x_shard).float().cpu()
+            torch.testing.assert_close(outs[mode], want, atol=6e-2, rtol=3e-2, msg=lambda m: f"{mode}: {m}")
+        torch.testing.assert_close(outs["peer_exchange"], outs["allreduce_tmp"], atol=2e-2, rtol=2e-2)
+        none = slots < 0
+        assert torch.equal(outs["peer_exchange"][none], outs["allreduce_tmp"][none]), "rows without adapter differ between modes"
+        assert N.device_status() == 0
+        results[rank] = "ok"
+    except Exception as exc:  # surfaced by the parent
+        results[rank] = f"{type(exc).__name__}: {exc}"[:600]
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_two_rank_tensor_parallel_on_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    assert dict(results) == {0: "ok", 1: "ok"}, dict(results)
