@@ -62,7 +62,7 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "linear", "backbone"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "linear", "backbone", "tp"],
                     help="decode = the headline decode BGMV layer; prefill = prefill SGMV add (tcgen05 kernels) of one "
                          "layer; linear = base GEMM + LoRA in one tensor-core kernel for the same layer; backbone = whole "
                          "decoder steps (prefill + graph-replayed decode) around the LoRA linears")
@@ -537,9 +537,11 @@ def run_prefill_arm(args):
     if linear:
         try:
             with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-                tf_peak, tkind = float(json.load(f)["bf16_tflops"]), "measured burst"
+                peaks = json.load(f)
+            tf_peak, tkind = float(peaks["bf16_tflops"]), "measured burst"
+            tf_sustained = float(peaks.get("bf16_tflops_sustained", 0.0)) or None
         except Exception:
-            tf_peak, tkind = 1590.0, "fallback"
+            tf_peak, tkind, tf_sustained = 1590.0, "fallback", 1400.0
         for i in range(3):  # cuBLAS handle / heuristics outside the timed region
             [unfused(d) for _, _, d in sets[i & 1]]
         unf = timed(lambda i: [unfused(d) for _, _, d in sets[i & 1]], max(3, args.steps // 2))
@@ -548,7 +550,11 @@ def run_prefill_arm(args):
                      "unit": "TFLOP/s", "gpu_launches": 2 * len(names) * args.steps,
                      "roofline": {"bound": "tensor", "achieved": ach, "peak": tf_peak, "unit": "TFLOP/s",
                                   "frac": ach / tf_peak, "traffic": None, "peak_kind": f"of {tkind}",
-                                  "kernel": "tc_tile_kernel", "algorithmic_flops_per_step": base_flops + lora_flops},
+                                  "kernel": "tc_tile_kernel", "algorithmic_flops_per_step": base_flops + lora_flops,
+                                  # the step runs back to back for longer than a burst; with sw_power_cap active
+                                  # the sustained cuBLAS figure is the comparable one
+                                  "frac_of_sustained_peak": (ach / tf_sustained) if tf_sustained else None,
+                                  "sustained_peak": tf_sustained},
                      "cublas_plus_prefill_add_ms_per_step": unf})
     else:
         ach = bytes_step / (ms_per_step * 1e-3) / 1e9
@@ -736,8 +742,82 @@ def run_backbone_arm(args):
     }))
 
 
+# ------------------------------------------------------------------ tensor-parallel row-parallel projection
+def run_tp_arm(args):
+    """Launched with torchrun on N >= 2 GPUs: the `down` projection of an 8-GPU-class layer (hidden 4096,
+    intermediate 14336, rank 64) as a row-parallel layer over N ranks, decode batch of 512 rows, in the three
+    exchange modes, and the exchange of the [T, r] partials alone (peer-memory kernel vs NCCL)."""
+    import torch.distributed as dist
+
+    from nanovllm_voxcpm_b200 import _native as N
+    from nanovllm_voxcpm_b200 import context as CTX
+    from nanovllm_voxcpm_b200 import layers as L
+    from nanovllm_voxcpm_b200.tp_exchange import TpExchange
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise RuntimeError("--workload tp needs torchrun with at least two ranks")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=device)
+    T, hidden, inter, S, r = 512, 4096, 14336, 32, 64
+    ex = TpExchange(capacity=8704 * r)
+
+    def timed(fn, reps):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(reps):
+            fn()
+        e.record()
+        e.synchronize()
+        t = torch.tensor([s.elapsed_time(e) / reps * 1e3], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    exchange = {}
+    for name, rows in (("decode_512x64", 512), ("prefill_8704x64", 8704)):
+        part = torch.randn(rows * r, device=device)
+        exchange[name] = {"peer_kernel_us": timed(lambda: ex.all_reduce_(part), 200),
+                          "nccl_us": timed(lambda: dist.all_reduce(part), 200), "bytes": rows * r * 4}
+    gen = torch.Generator().manual_seed(0)
+    slots = torch.randint(-1, S, (T,), generator=gen, dtype=torch.int32).to(device)
+    CTX.set_lora_context(CTX.build_lora_context_from_token_to_slot(slots))
+    x = torch.randn(T, inter // world, device=device).to(torch.bfloat16)
+    layer_us = {}
+    for mode in ("partial_y", "allreduce_tmp", "peer_exchange"):
+        layer = L.LoRARowParallelLinear(inter, hidden, max_loras=S, max_lora_rank=r, lora_tp_mode=mode).to(device, torch.bfloat16)
+        layer.tp_exchange = ex
+        with torch.no_grad():
+            layer.weight.normal_(0, 0.02)
+            layer.lora_A.normal_(0, 0.02)
+            layer.lora_B.normal_(0, 0.02)
+        for s in range(S):
+            layer._effective_lora_rank_values[s] = r
+        with torch.inference_mode():
+            layer_us[mode] = timed(lambda: layer(x), 100)
+        del layer
+    status = N.device_status()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "row-parallel multi-LoRA projection us per call (tensor parallel)", "value": layer_us["peer_exchange"],
+            "unit": "us", "n_gpus": world, "steps": 100, "warmup": 5, "ms_per_step": layer_us["peer_exchange"] * 1e-3,
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"down projection {inter} -> {hidden} sharded over {world} ranks, {T} rows, {S} adapters rank {r}"},
+            "layer_us_by_mode": layer_us, "exchange_us": exchange, "device_status": status,
+        }))
+    dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
+    if args.workload == "tp":
+        return run_tp_arm(args)
     if args.workload == "backbone" and args.impl in ("b200", "reference-gpu"):
         return run_backbone_arm(args)
     if args.impl == "reference":

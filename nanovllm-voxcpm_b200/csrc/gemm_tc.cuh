@@ -25,11 +25,19 @@
 namespace b200lora {
 
 constexpr int kTileThreads = 224;  // warp 0 TMA, warp 1 MMA + TMEM owner, warps 2-5 epilogue, warp 6 row mask
-constexpr int kTileSMs = 148;      // SMs of a B200: the schedule below is sized for them
-constexpr int kGemmStages = 3;
+constexpr int kStatusBadSmemBase = 4;  // device status bit: dynamic shared memory was not 1024-byte aligned
+constexpr int kTileSMs = 148;      // SMs of a B200: one persistent CTA each
+constexpr int kTileMaxSeg = 3;     // row blocks one CTA's tile range may touch
+#ifndef B200_GEMM_STAGES
+#define B200_GEMM_STAGES 4
+#endif
+#ifndef B200_GEMM_OUTBUFS
+#define B200_GEMM_OUTBUFS 2
+#endif
+constexpr int kGemmStages = B200_GEMM_STAGES;
 constexpr int kGemmStageBytes = kSgmvBM * kSgmvBK * 2 + kSgmvBN * kSgmvBK * 2;  // 48 KB: x tile + W tile
 constexpr int kGemmOutChunk = 64;                                               // columns per TMA store box
-constexpr int kGemmOutBufs = 4;
+constexpr int kGemmOutBufs = B200_GEMM_OUTBUFS;
 constexpr int kGemmOutBufBytes = kSgmvBM * kGemmOutChunk * 2;                   // 16 KB
 
 struct GemmArgs {
@@ -69,16 +77,35 @@ __device__ __forceinline__ void bulk_wait_group_read() {
 __global__ void __launch_bounds__(kTileThreads, 1)
 tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  __shared__ int s_slot[kSgmvBM], run_slot[kSgmvBM], run_lo[kSgmvBM], run_hi[kSgmvBM];
-  __shared__ int nruns_s, clean_s;
+  // run tables of the (at most kTileMaxSeg) row blocks this CTA's tile range touches; compact types:
+  // the stages leave no room for more than 3 KB of static shared memory
+  __shared__ int16_t s_slot[kTileMaxSeg][kSgmvBM], run_slot[kTileMaxSeg][kSgmvBM];
+  __shared__ uint8_t run_lo[kTileMaxSeg][kSgmvBM], run_hi[kTileMaxSeg][kSgmvBM];
+  __shared__ int seg_nruns[kTileMaxSeg];
   __shared__ __align__(8) uint64_t bars[3 * kGemmStages + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int blk = blockIdx.x, z = blockIdx.y, Z = gridDim.y;
   const int r = a.r_max, n = a.n;
-  const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;
+  // Persistent schedule: the output tiles, numbered row block major (id = blk * ntile_all + j), are
+  // dealt to the CTAs in equal contiguous ranges, so every SM gets the same number of tiles and a CTA
+  // changes row block at most kTileMaxSeg - 1 times.
+  const int ntile_all = (a.n_total + kSgmvBN - 1) / kSgmvBN;
+  const int nblk_all = (a.T + kSgmvBM - 1) / kSgmvBM;
+  const int total_tiles = nblk_all * ntile_all;
+  const int per_cta = (total_tiles + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int t_begin = min((int)blockIdx.x * per_cta, total_tiles), t_end = min(t_begin + per_cta, total_tiles);
+  const int blk_first = t_begin / ntile_all;
+  const int nseg = t_end > t_begin ? (t_end - 1) / ntile_all - blk_first + 1 : 0;  // <= kTileMaxSeg (host)
+  // The stages and output buffers fill the whole dynamic allocation (no alignment slack fits beside
+  // four 48 KB stages), so the 1024-byte alignment the swizzled tiles need must come from the
+  // declaration above; a base that is not aligned is reported instead of used.
+  const uint32_t smem_base = smem_u32(smem);
+  if ((smem_base & 1023u) != 0) {
+    if (tid == 0) atomicOr(&g_b200_status, kStatusBadSmemBase);
+    return;
+  }
   const uint32_t out_base = smem_base + kGemmStages * kGemmStageBytes;
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * (uint32_t)s; };
@@ -99,26 +126,26 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
     tmem_alloc(smem_u32(&tmem_base_s), (uint32_t)tmem_cols);
     tc_fence_before_sync();
   }
-  if (a.token_to_slot != nullptr && (a.lora || a.expand_mode)) {
-    sgmv_find_runs(a.token_to_slot, a.T, a.S, blk, s_slot, run_slot, run_lo, run_hi, &nruns_s);
-    if (tid == 0) {
-      const int nvalid = min(kSgmvBM, a.T - blk * kSgmvBM);
-      int covered = 0;
-      for (int u = 0; u < nruns_s; ++u) covered += run_hi[u] - run_lo[u];
-      clean_s = covered == nvalid;  // every in-range row has an adapter
+  const bool with_runs = a.token_to_slot != nullptr && (a.lora || a.expand_mode);
+  for (int sg = 0; sg < nseg; ++sg) {
+    if (with_runs) {
+      sgmv_find_runs(a.token_to_slot, a.T, a.S, blk_first + sg, s_slot[sg], run_slot[sg], run_lo[sg], run_hi[sg], &seg_nruns[sg]);
+    } else if (tid == 0) {
+      seg_nruns[sg] = 0;
     }
-  } else if (tid == 0) {
-    nruns_s = 0;
-    clean_s = 0;
   }
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
-  // EXPAND mode has nothing to add to a block without any adapter row
-  const bool active = !a.expand_mode || nruns_s > 0;
-  const int nruns = active ? nruns_s : 0;
-  const int ntile = active ? (a.n_total + kSgmvBN - 1) / kSgmvBN : 0;
   const int nk = a.expand_mode ? 0 : a.in_dim / kSgmvBK;
+  // tiles [ja, jb) of segment sg; EXPAND mode has nothing to add to a block without any adapter row
+  auto seg_range = [&](int sg, int& blk, int& ja, int& jb, int& nruns) {
+    blk = blk_first + sg;
+    nruns = seg_nruns[sg];
+    ja = max(t_begin - blk * ntile_all, 0);
+    jb = min(t_end - blk * ntile_all, ntile_all);
+    if (a.expand_mode && nruns == 0) jb = ja;
+  };
   const int row_bytes = r * 2;
   const uint32_t t_tile_bytes = (uint32_t)kSgmvBM * r * 2, b_tile_bytes = (uint32_t)kSgmvBN * r * 2;
 
@@ -128,7 +155,10 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
     if (lane == 0) {
       tma_prefetch_desc(&maps.x); tma_prefetch_desc(&maps.w); tma_prefetch_desc(&maps.t); tma_prefetch_desc(&maps.y);
       int st = 0, round = 0;
-      for (int j = z; j < ntile; j += Z) {
+      for (int sg = 0; sg < nseg; ++sg) {
+      int blk, ja, jb, nruns;
+      seg_range(sg, blk, ja, jb, nruns);
+      for (int j = ja; j < jb; ++j) {
         for (int kc = 0; kc < nk; ++kc) {
           if (round > 0) mbar_wait_bounded(empty_bar(st), (uint32_t)((round & 1) ^ 1), &abort_flag);
           const uint32_t base = smem_base + (uint32_t)st * kGemmStageBytes;
@@ -138,7 +168,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
           if (++st == kGemmStages) { st = 0; ++round; }
         }
         for (int u = 0; u < nruns; ++u) {
-          const int slot = run_slot[u];
+          const int slot = run_slot[sg][u];
           for (int s = 0; s < n; ++s) {
             const int lo = max(a.col[s], j * kSgmvBN), hi = min(a.col[s] + a.out[s], (j + 1) * kSgmvBN);
             if (lo >= hi) continue;
@@ -151,11 +181,15 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
           }
         }
       }
+      }
     }
   } else if (warp == 6) {
     // mask warp: zero the tmp rows outside the current run, then hand the stage to the MMA thread
     int st = 0, round = 0;
-    for (int j = z; j < ntile; j += Z) {
+    for (int sg = 0; sg < nseg; ++sg) {
+    int blk, ja, jb, nruns;
+    seg_range(sg, blk, ja, jb, nruns);
+    for (int j = ja; j < jb; ++j) {
       // (the masked barrier of a stage completes one phase per LoRA use of that stage; the MMA
       //  thread keeps the same per-stage phase bits)
       // Base stages need no masking, but their full barriers are still waited for: a waiter that
@@ -166,7 +200,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
         if (++st == kGemmStages) { st = 0; ++round; }
       }
       for (int u = 0; u < nruns; ++u) {
-        const int lo_row = run_lo[u], hi_row = run_hi[u];
+        const int lo_row = run_lo[sg][u], hi_row = run_hi[sg][u];
         for (int s = 0; s < n; ++s) {
           const int lo = max(a.col[s], j * kSgmvBN), hi = min(a.col[s] + a.out[s], (j + 1) * kSgmvBN);
           if (lo >= hi) continue;
@@ -187,12 +221,16 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
         }
       }
     }
+    }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_base = umma_idesc_bf16(kSgmvBM, kSgmvBN);
       int st = 0, round = 0, job = 0;
       uint32_t mphase = 0;  // bit st: parity of the next phase of masked_bar(st)
-      for (int j = z; j < ntile; j += Z, ++job) {
+      for (int sg = 0; sg < nseg; ++sg) {
+      int blk, ja, jb, nruns;
+      seg_range(sg, blk, ja, jb, nruns);
+      for (int j = ja; j < jb; ++j, ++job) {
         const int buf = job & 1;
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kSgmvBN);
         if (job >= 2) mbar_wait_bounded(acc_empty(buf), (uint32_t)(((job >> 1) - 1) & 1), &abort_flag);
@@ -232,16 +270,20 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
         }
         umma_commit(acc_full(buf));
       }
+      }
     }
   } else if (warp >= 2 && warp <= 5) {
     // epilogue warps: thread <-> row of the tile
     const int quarter = warp & 3;
     const int row_in_blk = quarter * 32 + lane;
     const int etid = tid - 64;  // 0..127
-    // EXPAND mode: this thread's row has no adapter -> its delta is -0.0 (see the header comment)
-    const bool neg_zero_row = a.expand_mode && s_slot[row_in_blk] < 0;
     int job = 0, chunk_no = 0;
-    for (int j = z; j < ntile; j += Z, ++job) {
+    for (int sg = 0; sg < nseg; ++sg) {
+    int blk, ja, jb, nruns;
+    seg_range(sg, blk, ja, jb, nruns);
+    // EXPAND mode: this thread's row has no adapter -> its delta is -0.0 (see the header comment)
+    const bool neg_zero_row = a.expand_mode && s_slot[sg][row_in_blk] < 0;
+    for (int j = ja; j < jb; ++j, ++job) {
       const int buf = job & 1;
       mbar_wait_bounded(acc_full(buf), (uint32_t)((job >> 1) & 1), &abort_flag);
       tc_fence_after_sync();
@@ -291,6 +333,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
       tc_fence_before_sync();
       mbar_arrive(acc_empty(buf));
     }
+    }
     if (etid == 0) bulk_wait_group_read<0>();
   }
   __syncthreads();
@@ -299,7 +342,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
 }
 
 // ------------------------------------------------------------------ host side
-inline size_t tc_tile_smem_bytes() { return (size_t)kGemmStages * kGemmStageBytes + kGemmOutBufs * kGemmOutBufBytes + 1024; }
+inline size_t tc_tile_smem_bytes() { return (size_t)kGemmStages * kGemmStageBytes + kGemmOutBufs * kGemmOutBufBytes; }
 
 // Slices must tile the packed output contiguously in 64-column units for the reduce path.
 inline bool tc_expand_fast_path_ok(const SgmvArgs& a) {
@@ -343,20 +386,17 @@ inline int tc_tile_prepare(const SgmvMaps& sm, const SgmvArgs& sa, const void* w
 
 inline int tc_tile_launch(const GemmMaps& maps, const GemmArgs& a, cudaStream_t stream) {
   const size_t smem = tc_tile_smem_bytes();
+  if (a.S > 32767) return fail(B200_LORA_EUNSUPPORTED, "tile kernel: more than 32767 adapter slots");
   if (int rc = sgmv_set_smem(reinterpret_cast<const void*>(tc_tile_kernel), smem)) return rc;
   const int nblk = (a.T + kSgmvBM - 1) / kSgmvBM;
   const int ntile = (a.n_total + kSgmvBN - 1) / kSgmvBN;
-  // Column tiles of a row block are dealt to Z CTAs. One CTA fits per SM, so the grid runs in
-  // ceil(nblk * Z / SMs) rounds of ceil(ntile / Z) tiles each; pick the Z with the shortest schedule
-  // (half a tile charged per round for the prologue of a CTA).
-  int Z = 1;
-  double best = 1e30;
-  for (int z = 1; z <= ntile; ++z) {
-    const int rounds = (nblk * z + kTileSMs - 1) / kTileSMs;
-    const double cost = rounds * ((ntile + z - 1) / z + 0.5);
-    if (cost < best - 1e-9) { best = cost; Z = z; }
-  }
-  tc_tile_kernel<<<dim3(nblk, Z), kTileThreads, smem, stream>>>(maps, a);
+  // One CTA per SM over equal contiguous tile ranges; more CTAs only when a range would otherwise
+  // touch more than kTileMaxSeg row blocks (few column tiles per block and very many blocks).
+  const int total = nblk * ntile;
+  int ncta = std::min(kTileSMs, total);
+  const int max_per = (kTileMaxSeg - 1) * ntile;
+  if ((total + ncta - 1) / ncta > max_per) ncta = (total + max_per - 1) / max_per;
+  tc_tile_kernel<<<ncta, kTileThreads, smem, stream>>>(maps, a);
   return check_launch("tc_tile_kernel");
 }
 

@@ -44,15 +44,17 @@ struct SgmvMaps {
 };
 
 // Runs of equal slot inside block `blk`, written to shared memory by thread 0.
-__device__ __forceinline__ void sgmv_find_runs(const int32_t* tts, int T, int S, int blk, int* s_slot, int* run_slot,
-                                               int* run_lo, int* run_hi, int* nruns) {
+// (table element types are the caller's: slot ids fit int16 for S <= 32767, row bounds 0..128 fit uint8)
+template <typename TS, typename TR>
+__device__ __forceinline__ void sgmv_find_runs(const int32_t* tts, int T, int S, int blk, TS* s_slot, TS* run_slot,
+                                               TR* run_lo, TR* run_hi, int* nruns) {
   const int row0 = blk * kSgmvBM;
   for (int i = threadIdx.x; i < kSgmvBM; i += blockDim.x) {
     const int row = row0 + i;
     int sl = -1;
     if (row < T) sl = tts[row];
     if (sl >= S) sl = -1;
-    s_slot[i] = sl;
+    s_slot[i] = (TS)sl;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -62,7 +64,7 @@ __device__ __forceinline__ void sgmv_find_runs(const int32_t* tts, int T, int S,
       if (sl < 0) { ++i; continue; }
       int j = i + 1;
       while (j < kSgmvBM && s_slot[j] == sl) ++j;
-      run_slot[n] = sl; run_lo[n] = i; run_hi[n] = j; ++n;
+      run_slot[n] = (TS)sl; run_lo[n] = (TR)i; run_hi[n] = (TR)j; ++n;
       i = j;
     }
     *nruns = n;
