@@ -230,12 +230,17 @@ int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T,
     // batches to the fused kernel, everything else (other dtypes, odd shapes) to the generic one.
     int n_act = 0;
     for (int s = 0; s < st.n; ++s) n_act += st.out[s] > 0;
-    if (dtype == B200_LORA_BF16 && T >= kSgmvAutoMinTokens && sgmv_supported(sp, nullptr) && workspace != nullptr &&
-        workspace_bytes >= sgmv_workspace_bytes(T, n_act, r_max))
-      impl = B200_LORA_IMPL_SGMV;
-    else if (dtype == B200_LORA_BF16 && have_buckets &&
+    const bool bgmv_ok = dtype == B200_LORA_BF16 && have_buckets &&
              (g_decode_kernel == 2 ? bgmv_split_supported(bp, nullptr)
-                                   : (bgmv_supported(bp, nullptr) || (g_decode_kernel == 0 && bgmv_split_supported(bp, nullptr)))))
+                                   : (bgmv_supported(bp, nullptr) || (g_decode_kernel == 0 && bgmv_split_supported(bp, nullptr))));
+    // The prefill kernels tile rows in token order and pay one stage per run of equal slot, so they
+    // want request-contiguous rows: with bucket arrays at hand, fewer than 32 rows per bucket on
+    // average means a decode-like batch (slots scattered over the rows) and goes to the bucket kernel.
+    const bool scattered = bgmv_ok && T < 32 * n_buckets;
+    if (dtype == B200_LORA_BF16 && T >= kSgmvAutoMinTokens && !scattered && sgmv_supported(sp, nullptr) &&
+        workspace != nullptr && workspace_bytes >= sgmv_workspace_bytes(T, n_act, r_max))
+      impl = B200_LORA_IMPL_SGMV;
+    else if (bgmv_ok)
       impl = B200_LORA_IMPL_BGMV;
     else
       impl = B200_LORA_IMPL_GENERIC;

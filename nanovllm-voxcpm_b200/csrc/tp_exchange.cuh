@@ -68,9 +68,9 @@ __global__ void __launch_bounds__(kTpThreads) tp_allreduce_kernel(const TpExchan
     float4* dst = reinterpret_cast<float4*>(a.recv[peer] + slot);
     for (int i = lo + tid; i < hi; i += kTpThreads) dst[i] = src[i];
   }
-  __threadfence_system();
+  // 2. publish: one flag per (source rank, CTA chunk) on every rank. The CTA barrier orders every
+  //    thread's stores before the publishing threads, whose release at system scope is cumulative.
   __syncthreads();
-  // 2. publish: one flag per (source rank, CTA chunk) on every rank
   if (tid < a.tp) st_release_sys(a.flags[tid] + ((size_t)par * a.tp + a.rank) * kTpMaxCtas + cta, epoch);
   // 3. wait for the same chunk of every source rank (bounded)
   if (tid < a.tp) {
