@@ -231,6 +231,31 @@ int lora_b200_tp_allreduce(const float* partial, float* out, int32_t count, void
                            int32_t rank, int32_t tp, int32_t capacity, void* stream);
 size_t lora_b200_tp_exchange_bytes(int32_t tp, int32_t capacity);
 
+/*
+ * Row-parallel (o / down) multi-LoRA add of one tensor-parallel rank:
+ *   tmp = scaling * x_shard . A_shard^T      (bucket kernel in shrink-only form, fp32 [n, T, r_max])
+ *   tmp = sum of tmp over the tp ranks       (lora_b200_tp_allreduce over peer memory)
+ *   y_partial[:, col_offsets ..] += tmp . B_shard^T   (bucket kernel in expand-only form)
+ * with lora_A sharded on the input dim and lora_B on the OUTPUT dim, so each rank reads 1/tp of B and
+ * the base output's own [T, out] all-reduce assembles the delta exactly once. The reference keeps B
+ * whole on every rank and lets the partial delta ride that all-reduce
+ * (nanovllm_voxcpm/layers/lora.py:714-742).
+ *  x, a_slabs   this rank's input shard [T, in/tp] and lora_A shards [S, r_max, in/tp]
+ *  b_slabs      this rank's lora_B shards [S, out_s/tp, r_max]; col_offsets: their first y column
+ *  tmp          device float[n_slices * T * r_max] scratch (n_slices * T * r_max % 4 == 0)
+ *  peer_buffers, rank, tp, capacity   as lora_b200_tp_allreduce (ignored for tp == 1)
+ * Other arguments as lora_b200_add (no zero-width slices). bf16 with bucket arrays runs the fused decode
+ * kernel's two halves; everything else one-CTA-per-token kernels.
+ */
+int lora_b200_shrink_allreduce_expand(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
+                                      int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
+                                      const int32_t* out_sizes, const int32_t* col_offsets, int32_t S, int32_t r_max,
+                                      const int32_t* rank_per_slot, const float* scale_per_slot,
+                                      const int32_t* token_to_slot, const int32_t* sorted_idx, const int32_t* slot_ids,
+                                      const int32_t* counts, const int32_t* offsets, int32_t n_buckets, float scaling,
+                                      int32_t dtype, float* tmp, void* const* peer_buffers, int32_t rank, int32_t tp,
+                                      int32_t capacity, void* stream);
+
 /* Tuning knobs of the fused decode kernel (process-wide, read at launch time). */
 #define B200_LORA_OPT_CLUSTER 1 /* CTAs per slot bucket: 1, 2, 4, 8; 0 = choose from n_buckets */
 #define B200_LORA_OPT_PDL 2     /* 1 = launch with programmatic stream serialization (default), 0 = off */

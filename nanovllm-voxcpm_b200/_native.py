@@ -68,6 +68,12 @@ _SIGNATURES = {
         c_int32, [c_void_p, c_void_p, c_int32, POINTER(c_void_p), c_int32, c_int32, c_int32, c_void_p],
     ),
     "lora_b200_tp_exchange_bytes": (c_size_t, [c_int32, c_int32]),
+    "lora_b200_shrink_allreduce_expand": (
+        c_int32,
+        [c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32, POINTER(c_void_p), POINTER(c_void_p),
+         POINTER(c_int32), POINTER(c_int32), c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_int32, c_float, c_int32, c_void_p, POINTER(c_void_p), c_int32, c_int32, c_int32, c_void_p],
+    ),
     "lora_b200_set_option": (c_int32, [c_int32, c_int32]),
     "lora_b200_device_status": (c_int32, [POINTER(c_int32), c_int32]),
 }

@@ -184,6 +184,69 @@ size_t lora_b200_workspace_bytes(int32_t T, int32_t n_slices, int32_t r_max) {
   return sgmv_workspace_bytes(T, n_slices, r_max);
 }
 
+int lora_b200_shrink_allreduce_expand(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
+                                      int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
+                                      const int32_t* out_sizes, const int32_t* col_offsets, int32_t S, int32_t r_max,
+                                      const int32_t* rank_per_slot, const float* scale_per_slot,
+                                      const int32_t* token_to_slot, const int32_t* sorted_idx, const int32_t* slot_ids,
+                                      const int32_t* counts, const int32_t* offsets, int32_t n_buckets, float scaling,
+                                      int32_t dtype, float* tmp, void* const* peer_buffers, int32_t rank, int32_t tp,
+                                      int32_t capacity, void* stream) {
+  if (!valid_dtype(dtype)) return fail(B200_LORA_EINVAL, "unknown dtype %d", dtype);
+  if (T < 0 || in_dim < 1 || S < 1 || r_max < 1)
+    return fail(B200_LORA_EINVAL, "bad sizes T=%d in=%d S=%d r_max=%d", T, in_dim, S, r_max);
+  if (T == 0) return B200_LORA_OK;
+  if (y == nullptr || x == nullptr || token_to_slot == nullptr || tmp == nullptr)
+    return fail(B200_LORA_EINVAL, "null y / x / token_to_slot / tmp");
+  if (out_sizes == nullptr || col_offsets == nullptr) return fail(B200_LORA_EINVAL, "null out_sizes / col_offsets");
+  if (tp < 1 || rank < 0 || rank >= tp) return fail(B200_LORA_EINVAL, "rank %d of %d", rank, tp);
+  if (tp > 1 && peer_buffers == nullptr) return fail(B200_LORA_EINVAL, "null peer_buffers with tp=%d", tp);
+  SliceTable st;
+  if (int rc = fill_slices(st, n_slices, a_slabs, b_slabs, out_sizes, col_offsets, true, true)) return rc;
+  int n_act = 0;
+  for (int s = 0; s < st.n; ++s) {
+    if (st.out[s] == 0) return fail(B200_LORA_EUNSUPPORTED, "tensor-parallel exchange: zero-width slice %d", s);
+    ++n_act;
+  }
+  const int64_t count64 = (int64_t)n_act * T * r_max;
+  if (count64 > (int64_t)INT32_MAX || (count64 & 3)) return fail(B200_LORA_EINVAL, "n_slices * T * r_max must be a multiple of 4 below 2^31");
+  const int count = (int)count64;
+  cudaStream_t st_ = static_cast<cudaStream_t>(stream);
+  const bool have_buckets = sorted_idx && slot_ids && counts && offsets && n_buckets > 0;
+
+  BgmvProblem bp;
+  bp.y = y; bp.y_ld = y_ld; bp.x = x; bp.x_ld = x_ld; bp.T = T; bp.in_dim = in_dim; bp.st = st;
+  bp.S = S; bp.r_max = r_max; bp.rank_per_slot = rank_per_slot; bp.scale_per_slot = scale_per_slot;
+  bp.sorted_idx = sorted_idx; bp.slot_ids = slot_ids; bp.counts = counts; bp.offsets = offsets;
+  bp.n_buckets = n_buckets; bp.scaling = scaling; bp.tmp_io = tmp;
+  BgmvProblem shrink_p = bp, expand_p = bp;
+  shrink_p.mode = 1;
+  expand_p.mode = 2; expand_p.scaling = 1.0f; expand_p.scale_per_slot = nullptr;  // the scale is already in tmp
+  const bool fused_kernels = dtype == B200_LORA_BF16 && have_buckets && bgmv_supported(shrink_p, nullptr) &&
+                             bgmv_supported(expand_p, nullptr);
+  if (fused_kernels) {
+    if (int rc = bgmv_launch(shrink_p, st_)) return rc;
+  } else {
+    // any dtype / shape: one CTA per token; rows without adapter are zero-filled (they are exchanged too)
+    if (r_max > 2048) return fail(B200_LORA_EUNSUPPORTED, "generic kernel: r_max=%d > 2048", r_max);
+    if (scale_per_slot != nullptr) return fail(B200_LORA_EUNSUPPORTED, "per-slot scales need the bf16 bucket kernels here");
+    int rc;
+    if (dtype == B200_LORA_BF16)
+      rc = launch_generic_shrink<__nv_bfloat16, float>(tmp, x, x_ld, T, in_dim, st, S, r_max, token_to_slot, scaling, st_);
+    else if (dtype == B200_LORA_F16)
+      rc = launch_generic_shrink<__half, float>(tmp, x, x_ld, T, in_dim, st, S, r_max, token_to_slot, scaling, st_);
+    else
+      rc = launch_generic_shrink<float, float>(tmp, x, x_ld, T, in_dim, st, S, r_max, token_to_slot, scaling, st_);
+    if (rc) return rc;
+  }
+  if (tp > 1)
+    if (int rc = tp_allreduce_launch(tmp, tmp, count, peer_buffers, rank, tp, capacity, st_)) return rc;
+  if (fused_kernels) return bgmv_launch(expand_p, st_);
+  if (dtype == B200_LORA_BF16) return launch_generic_expand<__nv_bfloat16, float>(y, y_ld, tmp, T, st, S, r_max, token_to_slot, 1, st_);
+  if (dtype == B200_LORA_F16) return launch_generic_expand<__half, float>(y, y_ld, tmp, T, st, S, r_max, token_to_slot, 1, st_);
+  return launch_generic_expand<float, float>(y, y_ld, tmp, T, st, S, r_max, token_to_slot, 1, st_);
+}
+
 int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
                   int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
                   const int32_t* out_sizes, const int32_t* col_offsets, int32_t S, int32_t r_max,

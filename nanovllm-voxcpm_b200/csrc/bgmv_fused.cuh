@@ -70,6 +70,10 @@ struct BgmvProblem {
   const int32_t* rank_per_slot; const float* scale_per_slot;
   const int32_t *sorted_idx, *slot_ids, *counts, *offsets;
   int n_buckets; float scaling;
+  // 0 = fused add; 1 = shrink only: tmp_io[s, t, 0:r] = scaling * x[t] . A_s[slot_t]^T (fp32, rows with an
+  // adapter only); 2 = expand only: y += tmp_io . B^T. The pair serves the tensor-parallel exchange of tmp.
+  int mode = 0;
+  float* tmp_io = nullptr;  // [n_slices, T, r_max] fp32
 };
 
 struct BgmvParams {
@@ -90,6 +94,8 @@ struct BgmvParams {
   int tmp_bytes;    // bytes of one tmp buffer
   int off_red, off_tmp, off_bar;
   int use_pdl;
+  int mode;         // 0 fused, 1 shrink only (tmp_io written), 2 expand only (tmp_io read)
+  float* tmp_io;
 };
 
 __host__ __device__ __forceinline__ int ceil_div_i(int a, int b) { return (a + b - 1) / b; }
@@ -153,7 +159,8 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
   const int Q = n * r_eff;                                       // stacked rank rows
   const int Rc = ((((Q + C - 1) >> p.c_shift) + 7) & ~7);        // rows owned per CTA
   const int q_lo = min(c * Rc, Q);
-  const int rows_c = min(q_lo + Rc, Q) - q_lo;                   // multiple of 8, may be 0
+  const int mode = p.mode;
+  const int rows_c = mode == 2 ? 0 : min(q_lo + Rc, Q) - q_lo;   // multiple of 8, may be 0 (expand only: no shrink rows)
   const int nt_c = rows_c >> 3;                                  // 8-row tiles of this CTA
   const int KP = p.KP, pitchA = p.pitchA, ER = p.ER, nkp = p.nkp;
   const int shrink_tiles = nt_c * nkp;
@@ -162,7 +169,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
 #pragma unroll
   for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) {
     e_lo[s] = e_n[s] = e_tiles[s] = 0;
-    if (s < n) {
+    if (s < n && mode != 1) {  // (shrink only: no expand tiles)
       const int out = p.st.out[s];
       e_lo[s] = min(c * p.oc[s], out);
       e_n[s] = min(e_lo[s] + p.oc[s], out) - e_lo[s];
@@ -218,7 +225,8 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
         if (i_qr >= r_eff) { i_qr = 0; ++i_qs; }
         if (i_j == nt_c) {
           i_j = 0; i_qs = q0_s; i_qr = q0_r;
-          if (++i_kp == nkp) { i_kp = 0; i_shrink = 0; i_s = 0; i_et = 0; }
+          // (shrink-only launches have no expand tiles: the next pass starts with shrink tiles again)
+          if (++i_kp == nkp) { i_kp = 0; i_shrink = tiles_exp > 0 ? 0 : 1; i_s = 0; i_et = 0; }
         }
       } else {
 #pragma unroll
@@ -404,9 +412,28 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
     }
     uint8_t* tmp_full = tmp_base + (size_t)(pass & 1) * p.tmp_bytes;
     const uint32_t tmp_ready_bar = tmp_ready_bars + 8u * (uint32_t)(pass & 1);
-    {
+    if (mode == 2) {
+      // expand only: tmp of this pass comes from global memory (fp32 [n, T, r_max], summed over the
+      // tensor-parallel ranks) and is rounded to bf16 into this CTA's own buffer
+      const int tok = tid >> 4;
+      int trow = -1;
+      if (pass * kBgmvTok + tok < cnt) trow = p.sorted_idx[start + pass * kBgmvTok + tok];
+      if (trow >= p.T) trow = -1;
+      for (int pr = tid & 15; pr < (Q >> 1); pr += 16) {
+        const int q = 2 * pr, s = q / r_eff, rr = q - s * r_eff;
+        float2 v = make_float2(0.f, 0.f);
+        if (trow >= 0) v = *reinterpret_cast<const float2*>(p.tmp_io + ((int64_t)s * p.T + trow) * p.r_max + rr);
+        *reinterpret_cast<uint32_t*>(tmp_full + (size_t)tok * p.pitchT + (size_t)q * 2) = pack_bf16x2(v.x, v.y);
+      }
+      named_bar_sync(1, kBgmvConsumers);
+    } else {
       const int half = rows_c >> 1;
       const int tok = tid >> 4;
+      int trow = -1;  // shrink only: token row of `tok`
+      if (mode == 1) {
+        if (pass * kBgmvTok + tok < cnt) trow = p.sorted_idx[start + pass * kBgmvTok + tok];
+        if (trow >= p.T) trow = -1;
+      }
       for (int pr = tid & 15; pr < half; pr += 16) {
         float s0 = 0.f, s1 = 0.f;
 #pragma unroll
@@ -415,18 +442,29 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
           s0 += v.x;
           s1 += v.y;
         }
-        const uint32_t v = pack_bf16x2(s0 * sc, s1 * sc);
-        const uint32_t laddr = smem_u32(tmp_full + (size_t)tok * p.pitchT + (size_t)(q_lo + 2 * pr) * 2);
-        for (int rc = 0; rc < C; ++rc) st_cluster_u32(mapa_shared(laddr, (uint32_t)rc), v);
+        if (mode == 1) {
+          // shrink only: fp32 result of this CTA's rank rows straight to global memory
+          const int q = q_lo + 2 * pr, s = q / r_eff, rr = q - s * r_eff;
+          if (trow >= 0)
+            *reinterpret_cast<float2*>(p.tmp_io + ((int64_t)s * p.T + trow) * p.r_max + rr) = make_float2(s0 * sc, s1 * sc);
+        } else {
+          const uint32_t v = pack_bf16x2(s0 * sc, s1 * sc);
+          const uint32_t laddr = smem_u32(tmp_full + (size_t)tok * p.pitchT + (size_t)(q_lo + 2 * pr) * 2);
+          for (int rc = 0; rc < C; ++rc) st_cluster_u32(mapa_shared(laddr, (uint32_t)rc), v);
+        }
       }
-    }
-    named_bar_sync(1, kBgmvConsumers);  // every store of this CTA is issued
-    if (tid < C) mbar_arrive_remote_release(mapa_shared(tmp_ready_bar, (uint32_t)tid));
-    if (pass == 0) { B200_TRACE_POINT(8) }
+      if (mode == 1) {
+        named_bar_sync(1, kBgmvConsumers);  // all warps have read the reduction buffer before the next pass refills it
+        continue;
+      }
+      named_bar_sync(1, kBgmvConsumers);  // every store of this CTA is issued
+      if (tid < C) mbar_arrive_remote_release(mapa_shared(tmp_ready_bar, (uint32_t)tid));
+      if (pass == 0) { B200_TRACE_POINT(8) }
 
-    // ===== expand: y[tok, cols] += tmp[16 tok, r] . B_rows^T ======================
-    mbar_wait_bounded_acquire_cluster(tmp_ready_bar, (uint32_t)((pass >> 1) & 1), abort_flag);
-    if (pass == 0) { B200_TRACE_POINT(9) }
+      // ===== expand: y[tok, cols] += tmp[16 tok, r] . B_rows^T ======================
+      mbar_wait_bounded_acquire_cluster(tmp_ready_bar, (uint32_t)((pass >> 1) & 1), abort_flag);
+      if (pass == 0) { B200_TRACE_POINT(9) }
+    }
     const uint32_t tmp_lo = smem_u32(tmp_full + (size_t)g * p.pitchT);
     const uint32_t tmp_hi = smem_u32(tmp_full + (size_t)(g + 8) * p.pitchT);
 
@@ -590,6 +628,9 @@ inline bool bgmv_plan(const BgmvProblem& b, BgmvParams* pp, const char** why) {
   p.off_tmp = p.off_red + red_bytes;
   p.off_bar = p.off_tmp + 2 * p.tmp_bytes;
   p.use_pdl = bgmv_options().pdl ? 1 : 0;
+  p.mode = b.mode;
+  p.tmp_io = b.tmp_io;
+  if (b.mode != 0 && b.tmp_io == nullptr) { *why = "shrink-only / expand-only need the tmp array"; return false; }
   if (pp != nullptr) *pp = p;
   return true;
 }

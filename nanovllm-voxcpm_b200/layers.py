@@ -491,6 +491,17 @@ class LoRARowParallelLinear(_LoRALayerBase):
         if token_to_slot is None:
             return y
         y_flat = y if y.dim() == 2 else y.view(-1, y.size(-1))
+        if self.lora_tp_mode == "peer_exchange" and x.is_cuda:
+            # one C call: bucket kernel (shrink half) -> peer-memory exchange -> bucket kernel (expand half)
+            if self.tp_exchange is None:
+                raise RuntimeError("lora_tp_mode='peer_exchange' needs a TpExchange in layer.tp_exchange")
+            metadata = self._runtime_metadata()
+            if metadata is None:
+                raise RuntimeError("LoRA metadata must be prepared by the model runner before backend execution")
+            widths, cols = self._slice_layout()
+            self.tp_exchange.row_parallel_add(y_flat, x_flat, [self.lora_A], [self.lora_B], widths, cols, metadata, 1.0,
+                                              rank_per_slot=self.effective_lora_rank)
+            return y
         tmp = torch.empty((1, x_flat.size(0), self.max_lora_rank), dtype=torch.float32, device=x.device)
         shrink_into(tmp, x_flat, [self.lora_A], token_to_slot, 1.0)
         if self.lora_tp_mode == "peer_exchange":

@@ -8,7 +8,7 @@ shrinks on its input shard, the ``[n, T, r]`` partials are summed here, and each
 its ``out / tp`` columns of ``lora_B``; the base output's own ``[T, out]`` all-reduce
 (``nanovllm_voxcpm/layers/lora.py:722-742``) then assembles the full delta exactly once.
 
-Every rank must call :meth:`all_reduce_` in the same order. Multicast is not used (plain peer stores).
+Every rank must issue the same sequence of exchanges. Multicast is not used (plain peer stores).
 """
 
 from __future__ import annotations
@@ -46,3 +46,49 @@ class TpExchange:
             N.check(N.lib().lora_b200_tp_allreduce(partial.data_ptr(), partial.data_ptr(), partial.numel(), self._peers,
                                                    self.rank, self.tp, self.capacity, N.current_stream(partial.device)))
         return partial
+
+    def row_parallel_add(self, y, x, a_slabs, b_slabs, out_sizes, col_offsets, metadata, scaling: float = 1.0, *,
+                         rank_per_slot=None, scale_per_slot=None) -> None:
+        """Shrink on this rank's input shard, sum the ``[n, T, r]`` partials over the group through peer
+        memory, expand this rank's output shard of ``lora_B`` into the partial ``y``: one C call, three
+        launches, no library collective."""
+        shrink_allreduce_expand(y, x, a_slabs, b_slabs, out_sizes, col_offsets, metadata, scaling,
+                                rank_per_slot=rank_per_slot, scale_per_slot=scale_per_slot, exchange=self)
+
+
+def shrink_allreduce_expand(y, x, a_slabs, b_slabs, out_sizes, col_offsets, metadata, scaling: float = 1.0, *,
+                            rank_per_slot=None, scale_per_slot=None, exchange: TpExchange | None = None) -> None:
+    """One ``lora_b200_shrink_allreduce_expand`` call; ``exchange=None`` is the single-rank form (no peers)."""
+    from .lora import _as_3d, _i32, scratch_for
+
+    N.require_cuda(y, x, *a_slabs, *b_slabs, metadata.token_to_slot)
+    if x.dim() != 2 or y.dim() != 2 or x.stride(1) != 1 or y.stride(1) != 1:
+        raise ValueError("x and y must be 2D with unit column stride")
+    a_slabs = [_as_3d(a) for a in a_slabs]
+    b_slabs = [_as_3d(b) for b in b_slabs]
+    T, in_dim = x.shape
+    S, r_max, _ = a_slabs[0].shape
+    n = len(a_slabs)
+    peers, rank, tp, capacity = None, 0, 1, 4
+    if exchange is not None:
+        peers, rank, tp, capacity = exchange._peers, exchange.rank, exchange.tp, exchange.capacity
+        if tp > 1 and n * T * r_max > capacity:
+            raise ValueError(f"exchange of {n * T * r_max} values exceeds the capacity {capacity} of this TpExchange")
+    tts, srt, cnt, off, ids, _, _ = metadata.as_kernel_metadata(T)
+    n_buckets = 0
+    if srt is not None and ids is not None and cnt is not None and off is not None:
+        n_buckets = min(ids.numel(), cnt.numel(), off.numel() - 1)
+        if metadata.num_active_loras > 0:
+            n_buckets = min(n_buckets, metadata.num_active_loras)
+    if n_buckets <= 0:
+        srt = ids = cnt = off = None
+        n_buckets = 0
+    tmp = scratch_for(x.device, n * T * r_max * 4 + 256)
+    tmp_ptr = (tmp.data_ptr() + 255) & ~255
+    with torch.cuda.device(x.device):
+        N.check(N.lib().lora_b200_shrink_allreduce_expand(
+            y.data_ptr(), y.stride(0), x.data_ptr(), x.stride(0), T, in_dim, n, N.ptr_array(a_slabs), N.ptr_array(b_slabs),
+            N.int_array(out_sizes), N.int_array(col_offsets), S, r_max, N.ptr(_i32(rank_per_slot, "rank_per_slot")),
+            N.ptr(scale_per_slot), N.ptr(_i32(tts, "token_to_slot")), N.ptr(_i32(srt, "sorted")), N.ptr(_i32(ids, "slot ids")),
+            N.ptr(_i32(cnt, "counts")), N.ptr(_i32(off, "offsets")), n_buckets, float(scaling), N.dtype_code(x.dtype),
+            tmp_ptr, peers, rank, tp, capacity, N.current_stream(x.device)))

@@ -54,6 +54,46 @@ def test_exchange_kernel_single_rank_counts_epochs_and_replays_in_a_graph():
         exchange(torch.zeros(6, device="cuda"))
 
 
+@pytest.mark.parametrize("name", ["qkv", "o", "gate_up", "down"])
+def test_shrink_and_expand_halves_of_the_decode_kernel_single_rank(name):
+    """tp = 1: shrink-only launch -> fp32 tmp in global memory -> expand-only launch must give what the
+    fused launch gives (same kernel, intermediate through memory instead of shared memory)."""
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "tests"))
+    from helpers import assert_lora_close
+    from nanovllm_voxcpm_b200 import _native as N
+    from nanovllm_voxcpm_b200 import batch_plan as BP
+    from nanovllm_voxcpm_b200 import lora as LORA
+    from nanovllm_voxcpm_b200 import workloads as W
+    from nanovllm_voxcpm_b200.tp_exchange import shrink_allreduce_expand
+    from oracle import lora_oracle as O
+
+    for seed, T, ranks in ((3, 256, None), (4, 300, "mixed")):  # 300 rows on 32 slots: some buckets take two passes
+        p = W.decode_projection(name, seed=seed, T=T)
+        if ranks:
+            p.ranks[:] = torch.tensor([(8, 16, 32)[s % 3] for s in range(32)], dtype=torch.int32)
+            for a, b in zip(p.a_slabs, p.b_slabs):
+                for s in range(32):
+                    a[s, int(p.ranks[s]):] = 0
+                    b[s, :, int(p.ranks[s]):] = 0
+        d = p.to_device("cuda")
+        ctx = BP.build_lora_context_from_batch_plan(
+            BP.build_lora_batch_plan_from_token_to_slot({}, p.token_to_slot.tolist()), device="cuda")
+        meta = LORA.LoRAMetadata(ctx.token_to_slot, ctx.token_indices_sorted_by_slot, ctx.active_slot_ids,
+                                 ctx.num_tokens_per_slot, ctx.slot_start_offsets, False, ctx.num_active_loras)
+        y = d.y.clone()
+        shrink_allreduce_expand(y, d.x, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets, meta, 1.0,
+                                rank_per_slot=d.ranks if ranks else None)
+        torch.cuda.synchronize()
+        ref = O.add_lora(p.y, p.x, p.a_slabs, p.b_slabs, p.token_to_slot, 1.0, p.col_offsets)
+        assert_lora_close(y.cpu(), ref, what=f"{name}: shrink-only + expand-only")
+        none = p.token_to_slot < 0
+        assert torch.equal(y.cpu()[none].view(torch.int16), p.y[none].view(torch.int16))
+    assert N.device_status() == 0
+
+
 def _worker(rank: int, world: int, port: int, results):
     import sys
 
@@ -110,7 +150,11 @@ def _worker(rank: int, world: int, port: int, results):
         for s, (a, b, sc) in adapters.items():
             O.write_slot(a_full, b_full, s, a.float(), b.float(), r, sc)
         want = O.linear_lora(x, w, None, [a_full.to(torch.bfloat16)], [b_full.to(torch.bfloat16)], [0], slots)
-        CTX.set_lora_context(CTX.build_lora_context_from_token_to_slot(slots.to(dev)))
+        from nanovllm_voxcpm_b200 import batch_plan as BP
+
+        # full metadata (bucket arrays): the peer_exchange mode then runs the bucket kernel's two halves
+        CTX.set_lora_context(BP.build_lora_context_from_batch_plan(
+            BP.build_lora_batch_plan_from_token_to_slot({}, slots.tolist()), device=dev))
         x_shard = x.chunk(world, 1)[rank].contiguous().to(dev)
         outs = {}
         for mode in ("partial_y", "allreduce_tmp", "peer_exchange"):
