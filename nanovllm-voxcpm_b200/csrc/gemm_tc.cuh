@@ -58,6 +58,30 @@ struct GemmMaps {
   CUtensorMap y;                            // [T, n_total]      box 128 x 64 (store / reduce)
 };
 
+// L2 cache policies: the output is written once and not read again by this kernel (evict first),
+// the weight tiles are re-read by every row block (evict last).
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap* tmap, int c0, int c1, uint32_t bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(dst_smem), "l"(tmap), "r"(c0), "r"(c1), "r"(bar), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* tmap, uint32_t src_smem, int c0, int c1, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(tmap),
+               "r"(src_smem), "r"(c0), "r"(c1), "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, uint32_t src_smem, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
                "r"(src_smem), "r"(c0), "r"(c1)
@@ -154,6 +178,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&maps.x); tma_prefetch_desc(&maps.w); tma_prefetch_desc(&maps.t); tma_prefetch_desc(&maps.y);
+      const uint64_t w_policy = l2_policy_evict_last();
       int st = 0, round = 0;
       for (int sg = 0; sg < nseg; ++sg) {
       int blk, ja, jb, nruns;
@@ -164,7 +189,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
           const uint32_t base = smem_base + (uint32_t)st * kGemmStageBytes;
           mbar_arrive_expect_tx(full_bar(st), kGemmStageBytes);
           tma_load_2d(base, &maps.x, kc * kSgmvBK, blk * kSgmvBM, full_bar(st));
-          tma_load_2d(base + kSgmvBM * kSgmvBK * 2, &maps.w, kc * kSgmvBK, j * kSgmvBN, full_bar(st));
+          tma_load_2d_hint(base + kSgmvBM * kSgmvBK * 2, &maps.w, kc * kSgmvBK, j * kSgmvBN, full_bar(st), w_policy);
           if (++st == kGemmStages) { st = 0; ++round; }
         }
         for (int u = 0; u < nruns; ++u) {
@@ -326,7 +351,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
         named_bar_sync(2, 128);
         if (etid == 0) {
           if (a.expand_mode) tma_reduce_add_2d(&maps.y, obuf, col0, blk * kSgmvBM);
-          else tma_store_2d(&maps.y, obuf, col0, blk * kSgmvBM);
+          else tma_store_2d_hint(&maps.y, obuf, col0, blk * kSgmvBM, l2_policy_evict_first());
           bulk_commit_group();
         }
       }
