@@ -189,6 +189,24 @@ int lora_b200_add_prefill_noalloc(void* y, int64_t y_ld, const void* x, int64_t 
  * the reference. */
 size_t lora_b200_static_scratch_bytes(void);
 
+/*
+ * Adapter admission in one launch. `staging` is the device copy of ONE packed buffer: `n_desc`
+ * 64-byte descriptors, then the payload tensors they point into (byte offsets from the start of
+ * the buffer). A descriptor either fills one slab region of the slot,
+ *     dst[i, j] = (i < src_rows && j < src_cols) ? round(float(src[i * src_ld + j]) * scale) : 0
+ * over dst_rows x dst_cols (the slot's [r_max, in] block of lora_A, or its [out, r_max] block of
+ * lora_B with scale = the adapter's scaling), or writes one int32 / float scalar (the slot's entries
+ * of effective_lora_rank / lora_scaling / lora_base_scaling). Layout of a descriptor, little endian:
+ *     u64 dst; i64 src_offset; i32 kind (0 region, 1 int32 scalar, 2 floating scalar of dst_dtype); i32 dst_rows, dst_cols;
+ *     i32 src_rows, src_cols, src_ld; i32 src_dtype, dst_dtype (B200_LORA_BF16 / F16 / F32);
+ *     f32 scale (kind 2: the value); i32 ivalue (kind 1: the value); 8 bytes padding.
+ * `max_elems` = largest dst_rows * dst_cols of the table.
+ * Replaces the per-module loop of `_load_lora_slot` + `set_slot_lora`
+ * (nanovllm_voxcpm/engine/model_runner.py:389-420, nanovllm_voxcpm/layers/lora.py:395-417): same slab
+ * contents, one host->device copy and one kernel instead of several per module.
+ */
+int lora_b200_load_slot(const void* staging, int32_t n_desc, int64_t max_elems, void* stream);
+
 /* conventions of lora_b200_build_metadata */
 #define B200_LORA_META_GRAPH 0  /* fixed buckets [-1, 0 .. S-1], bucket 0 always empty (CUDA-graph buffers) */
 #define B200_LORA_META_KERNEL 1 /* compact ids incl. the -1 bucket with its rows (LoRAKernelMeta.prepare_tensors) */

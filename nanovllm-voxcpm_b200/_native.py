@@ -64,6 +64,7 @@ _SIGNATURES = {
     "lora_b200_build_metadata": (
         c_int32, [c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     ),
+    "lora_b200_load_slot": (c_int32, [c_void_p, c_int32, c_int64, c_void_p]),
     "lora_b200_tp_allreduce": (
         c_int32, [c_void_p, c_void_p, c_int32, POINTER(c_void_p), c_int32, c_int32, c_int32, c_void_p],
     ),

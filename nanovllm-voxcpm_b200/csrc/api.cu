@@ -6,6 +6,7 @@
 #include "bgmv_split.cuh"
 #include "metadata.cuh"
 #include "tp_exchange.cuh"
+#include "slot_loader.cuh"
 #include "sgmv_tc.cuh"
 #include "gemm_tc.cuh"
 
@@ -120,6 +121,10 @@ int lora_b200_build_metadata(const int32_t* token_to_slot, int32_t T, int32_t S,
                              int32_t* info, void* stream) {
   return build_metadata(token_to_slot, T, S, convention, sorted_idx, slot_ids, counts, offsets, info,
                         static_cast<cudaStream_t>(stream));
+}
+
+int lora_b200_load_slot(const void* staging, int32_t n_desc, int64_t max_elems, void* stream) {
+  return slot_load_launch(staging, n_desc, max_elems, static_cast<cudaStream_t>(stream));
 }
 
 size_t lora_b200_tp_exchange_bytes(int32_t tp, int32_t capacity) { return tp_exchange_bytes(tp, capacity); }
