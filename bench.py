@@ -62,7 +62,7 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "linear", "backbone", "tp"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "linear", "backbone", "tp", "admission"],
                     help="decode = the headline decode BGMV layer; prefill = prefill SGMV add (tcgen05 kernels) of one "
                          "layer; linear = base GEMM + LoRA in one tensor-core kernel for the same layer; backbone = whole "
                          "decoder steps (prefill + graph-replayed decode) around the LoRA linears")
@@ -742,6 +742,85 @@ def run_backbone_arm(args):
     }))
 
 
+# ------------------------------------------------------------------ adapter admission (checkpoint -> resident slot)
+def run_admission_arm(args):
+    """One adapter (rank 32, every projection of a 24-layer decoder, fp32 payload of ~68 MB) admitted into a slot:
+    `SlotLoader.load_slot` (one descriptor table + the payload's pinned arena copied as it lies, one kernel) against
+    the module-by-module procedure of the reference's runner (per module: host->device copy per tensor, clear, copy
+    the used rows / columns, scale B). Wall clock per admission, device idle before and after."""
+    import tempfile
+
+    from nanovllm_voxcpm_b200 import _native as N
+    from nanovllm_voxcpm_b200 import adapter_checkpoint as AC
+    from nanovllm_voxcpm_b200 import backbone as BB
+    from nanovllm_voxcpm_b200 import layers as L
+    from nanovllm_voxcpm_b200.slot_loader import SlotLoader
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise RuntimeError("--workload admission is a single-GPU measurement")
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    cfg = BB.DecoderConfig(num_layers=args.layers, max_loras=8)
+    with torch.device(device):
+        model = BB.Decoder(cfg).to(torch.bfloat16)
+    modules = {n: m for n, m in model.named_modules() if isinstance(m, L._LORA_LAYER_TYPES)}
+    gen = torch.Generator().manual_seed(0)
+    rank, tensors = cfg.max_lora_rank, {}
+    unpack = {"qkv_proj": ("q_proj", "k_proj", "v_proj"), "gate_up_proj": ("gate_proj", "up_proj")}
+    for name, m in modules.items():
+        parent, _, leaf = name.rpartition(".")
+        for proj, a_slab, b_slab in zip(unpack.get(leaf, (leaf,)), m._a_slices(), m._b_slices()):
+            tensors[f"{parent}.{proj}.lora_A"] = torch.randn(rank, a_slab.size(2), generator=gen) * 0.05
+            tensors[f"{parent}.{proj}.lora_B"] = torch.randn(b_slab.size(1), rank, generator=gen) * 0.05
+    with tempfile.TemporaryDirectory() as root:
+        path = AC.save_lora_checkpoint(os.path.join(root, "adapter"), tensors, rank=rank, alpha=2.0 * rank)
+        AC.load_lora_checkpoint(str(path))
+        t0 = time.perf_counter()
+        payload = AC.load_lora_checkpoint(str(path))
+        read_ms = (time.perf_counter() - t0) * 1e3
+    payload_bytes = sum(t.numel() * 4 for t in tensors.values())
+    loader = SlotLoader(model)
+    loaded = {}
+
+    def by_module(slot):
+        for name in loaded.get(slot, []):
+            modules[name].clear_slot_lora(slot)
+        for name, mp in payload.modules.items():
+            b = mp.lora_b
+            modules[name].set_slot_lora(slot, mp.lora_a.to(device="cuda", non_blocking=True),
+                                        [t.to(device="cuda", non_blocking=True) for t in b] if isinstance(b, list)
+                                        else b.to(device="cuda", non_blocking=True), mp.effective_rank, mp.scaling)
+        loaded[slot] = list(payload.modules)
+
+    def wall(fn, reps, warm):
+        for i in range(warm):
+            fn(i % cfg.max_loras)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(reps):
+            fn(i % cfg.max_loras)
+            torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / reps * 1e3
+
+    reps, warm = args.steps, max(args.warmup, 3)
+    one_launch_ms = wall(lambda s: loader.load_slot(s, payload), reps, warm)
+    slabs = {n: [t.detach().clone() for t in (*m._a_slices(), *m._b_slices())] for n, m in modules.items()}
+    per_module_ms = wall(by_module, reps, warm)
+    same = all(torch.equal(a, b) for n, m in modules.items() for a, b in zip(slabs[n], (*m._a_slices(), *m._b_slices())))
+    print(json.dumps({
+        "metric": "adapter admission ms (checkpoint payload on the host -> resident slot)", "value": one_launch_ms,
+        "unit": "ms", "n_gpus": 1, "steps": reps, "warmup": warm, "ms_per_step": one_launch_ms, "higher_is_better": False,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"one rank-{rank} adapter over {len(modules)} modules of a {cfg.num_layers}-layer decoder, "
+                               f"{payload_bytes / 1e6:.1f} MB fp32 payload, bf16 slabs"},
+        "module_by_module_ms": per_module_ms, "speedup": per_module_ms / one_launch_ms,
+        "h2d_gbs": payload_bytes / (one_launch_ms * 1e-3) / 1e9, "checkpoint_read_ms": read_ms,
+        "slabs_identical": bool(same), "gpu_launches": reps, "device_status": N.device_status(),
+    }))
+
+
 # ------------------------------------------------------------------ tensor-parallel row-parallel projection
 def run_tp_arm(args):
     """Launched with torchrun on N >= 2 GPUs: the `down` projection of an 8-GPU-class layer (hidden 4096,
@@ -818,6 +897,8 @@ def main():
     args = parse_args()
     if args.workload == "tp":
         return run_tp_arm(args)
+    if args.workload == "admission":
+        return run_admission_arm(args)
     if args.workload == "backbone" and args.impl in ("b200", "reference-gpu"):
         return run_backbone_arm(args)
     if args.impl == "reference":

@@ -10,7 +10,9 @@ host mirrors are used unchanged.
 
 ``payload`` maps module names to ``(lora_a, lora_b, effective_rank, scaling)`` in the form each
 layer's ``set_slot_lora`` takes (multi-slice layers: ``lora_a [slices, rank, in]`` and a list of
-``lora_b``); tensors may live on the host (the usual case) or on the device.
+``lora_b``); tensors may live on the host (the usual case) or on the device. A ``LoRAModelPayload``
+(``adapter_checkpoint.load_lora_checkpoint``) is taken as it is; its tensors are views of one pinned
+arena, which is copied to the device in one piece without being repacked on the host.
 """
 
 from __future__ import annotations
@@ -65,9 +67,18 @@ class SlotLoader:
         return [lora_a], [lora_b]
 
     # ------------------------------------------------------------------ load
-    def load_slot(self, slot_id: int, payload: dict) -> None:
+    def load_slot(self, slot_id: int, payload) -> None:
+        arena = None
+        if hasattr(payload, "modules"):  # a LoRAModelPayload (adapter_checkpoint / the reference's dataclass)
+            arena = getattr(payload, "arena", None)
+            payload = {name: (m.lora_a, m.lora_b, m.effective_rank, m.scaling) for name, m in payload.modules.items()}
+        if arena is not None and (arena.device.type != "cpu" or arena.dtype != torch.uint8 or not arena.is_contiguous()):
+            arena = None
+        arena_lo = arena.data_ptr() if arena is not None else 0
+        arena_hi = arena_lo + (arena.numel() if arena is not None else 0)
         descs: list[_Desc] = []
-        blobs: list[tuple[int, torch.Tensor]] = []   # (byte offset, host tensor) of every payload tensor
+        in_arena: list[_Desc] = []                   # descriptors whose payload is read from the arena's copy
+        blobs: list[tuple[int, torch.Tensor]] = []   # (byte offset, host tensor) of every other payload tensor
         cursor = 0
         max_elems = 1
 
@@ -81,6 +92,13 @@ class SlotLoader:
             if src is None:
                 d.src_rows = d.src_cols = d.src_ld = 0
                 d.src_dtype, d.src_offset = N.dtype_code(torch.float32), 0
+            elif (arena is not None and src.device.type == "cpu" and src.dim() == 2 and src.stride(1) == 1
+                  and arena_lo <= src.data_ptr() and src.data_ptr() + src.element_size() * (
+                      (src.size(0) - 1) * src.stride(0) + src.size(1)) <= arena_hi):
+                # a view of the payload's arena: the arena is copied as it lies, nothing is repacked
+                d.src_rows, d.src_cols, d.src_ld = rows_used, cols_used, src.stride(0)
+                d.src_dtype, d.src_offset = N.dtype_code(src.dtype), src.data_ptr() - arena_lo
+                in_arena.append(d)
             else:
                 src = src.detach()
                 if src.device.type != "cpu":
@@ -132,10 +150,14 @@ class SlotLoader:
         table_bytes = len(descs) * 64
         if self._copied is not None:
             self._copied.synchronize()  # the previous admission's copy still reads the pinned buffer until then
-        host, dev = self._buffers(table_bytes + cursor)
+        # device layout: [descriptor table | repacked payload tensors | the arena as it lies on the host]
+        arena_base = (table_bytes + cursor + 63) & ~63
+        arena_bytes = arena.numel() if in_arena else 0
+        host, dev = self._buffers(arena_base + arena_bytes)
+        from_arena = {id(d) for d in in_arena}
         for d in descs:
             if d.kind == 0 and d.src_rows > 0:
-                d.src_offset += table_bytes
+                d.src_offset += arena_base if id(d) in from_arena else table_bytes
         table = (_Desc * len(descs))(*descs)
         host[:table_bytes].copy_(torch.frombuffer(bytearray(bytes(table)), dtype=torch.uint8))
         for off, src in blobs:
@@ -144,6 +166,9 @@ class SlotLoader:
         total = table_bytes + cursor
         with torch.cuda.device(self.device):
             dev[:total].copy_(host[:total], non_blocking=True)
+            if arena_bytes:
+                # asynchronous when the arena is pinned; the payload must stay unchanged until the copy has run
+                dev[arena_base: arena_base + arena_bytes].copy_(arena, non_blocking=True)
             self._copied = torch.cuda.Event()
             self._copied.record()
             N.check(N.lib().lora_b200_load_slot(dev.data_ptr(), len(descs), max_elems, N.current_stream(self.device)))

@@ -91,3 +91,37 @@ def test_batched_slot_load_equals_module_by_module_load():
     with pytest.raises(ValueError):
         bad = _adapter(model, 64, 1.0, seed=5)  # rank above max_lora_rank
         loader.load_slot(0, bad)
+
+
+def test_checkpoint_payload_is_admitted_from_its_arena(tmp_path):
+    """Checkpoint on disk -> one pinned arena -> slot: same slabs as loading the same payload module by module."""
+    from nanovllm_voxcpm_b200 import adapter_checkpoint as ac
+
+    cfg, model = _model()
+    ref = copy.deepcopy(model)
+    gen = torch.Generator().manual_seed(11)
+    rank, tensors = 16, {}
+    unpack = {"qkv_proj": ("q_proj", "k_proj", "v_proj"), "gate_up_proj": ("gate_proj", "up_proj")}
+    for name, m in model.named_modules():
+        if not isinstance(m, L._LORA_LAYER_TYPES):
+            continue
+        parent, _, leaf = name.rpartition(".")
+        for proj, a_slab, b_slab in zip(unpack.get(leaf, (leaf,)), m._a_slices(), m._b_slices()):
+            tensors[f"base_model.model.{parent}.{proj}.lora_A"] = (torch.randn(rank, a_slab.size(2), generator=gen) * 0.1).bfloat16()
+            tensors[f"base_model.model.{parent}.{proj}.lora_B"] = (torch.randn(b_slab.size(1), rank, generator=gen) * 0.1).bfloat16()
+    path = ac.save_lora_checkpoint(str(tmp_path / "adapter"), tensors, rank=rank, alpha=24.0)
+    payload = ac.load_lora_checkpoint(str(path))
+    assert payload.arena.is_pinned() and payload.modules.keys() == {n for n, m in model.named_modules()
+                                                                    if isinstance(m, L._LORA_LAYER_TYPES)}
+    loader = SlotLoader(model)
+    loader.load_slot(2, _adapter(model, 32, 1.0, seed=12))  # an occupant to replace
+    loader.load_slot(2, payload)
+    _load_by_module(ref, 2, {n: (m.lora_a, m.lora_b, m.effective_rank, m.scaling) for n, m in payload.modules.items()})
+    torch.cuda.synchronize()
+    got, want = _state(model), _state(ref)
+    for key in want:
+        if key.endswith(".host"):
+            assert got[key] == want[key], key
+        else:
+            assert torch.equal(got[key], want[key]), key
+    assert N.device_status() == 0
