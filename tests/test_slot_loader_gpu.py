@@ -116,7 +116,11 @@ def test_checkpoint_payload_is_admitted_from_its_arena(tmp_path):
     loader = SlotLoader(model)
     loader.load_slot(2, _adapter(model, 32, 1.0, seed=12))  # an occupant to replace
     loader.load_slot(2, payload)
-    _load_by_module(ref, 2, {n: (m.lora_a, m.lora_b, m.effective_rank, m.scaling) for n, m in payload.modules.items()})
+    loader.load_slot(0, payload)  # the same payload again: its cached descriptor table, aimed at another slot
+    assert len(loader._plans) == 1
+    by_name = {n: (m.lora_a, m.lora_b, m.effective_rank, m.scaling) for n, m in payload.modules.items()}
+    _load_by_module(ref, 2, by_name)
+    _load_by_module(ref, 0, by_name)
     torch.cuda.synchronize()
     got, want = _state(model), _state(ref)
     for key in want:
