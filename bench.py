@@ -60,9 +60,12 @@ def parse_args():
                          "baseline/_ref on the same workload, where that install and triton are usable")
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--glue", default="fused", choices=["fused", "torch"],
+                    help="backbone workload: the steps between the projections as this library's single-launch kernels "
+                         "(residual add + RMSNorm, RoPE + cache store, SiLU * up) or as plain torch ops")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "linear", "backbone", "tp", "admission"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "linear", "backbone", "tp", "admission", "glue"],
                     help="decode = the headline decode BGMV layer; prefill = prefill SGMV add (tcgen05 kernels) of one "
                          "layer; linear = base GEMM + LoRA in one tensor-core kernel for the same layer; backbone = whole "
                          "decoder steps (prefill + graph-replayed decode) around the LoRA linears")
@@ -700,6 +703,7 @@ def run_backbone_arm(args):
         model = BB.Decoder(cfg).to(torch.bfloat16)
     model.init_random_(0)
     model.fill_adapter_slots_(cfg.max_loras, cfg.max_lora_rank, seed=1)
+    model.fused_glue = args.glue == "fused" and args.impl == "b200"
     backend_name = "B200LoRABackend"
     if args.impl == "reference-gpu":
         # same decoder, same layers, but every LoRA call goes to the unmodified reference's own GPU backend
@@ -739,6 +743,115 @@ def run_backbone_arm(args):
         "adapter_overhead": {"decode": base["decode_tokens_per_s"] / lora["decode_tokens_per_s"],
                              "prefill": base["prefill_tokens_per_s"] / lora["prefill_tokens_per_s"]},
         "device_status": N.device_status(), "impl": args.impl, "lora_backend": backend_name,
+        "glue": "fused kernels" if model.fused_glue else "torch ops",
+    }))
+
+
+# ------------------------------------------------------------------ glue kernels between the projections
+def run_glue_arm(args):
+    """The three single-launch glue kernels on a prefill batch (8192 rows; hidden 1024, 16 q / 2 kv heads x 64,
+    intermediate 4096), each against the chain of torch ops it replaces. Every call works on the next of several
+    buffer sets that together exceed L2, so rows come from HBM; timed with CUDA events."""
+    from nanovllm_voxcpm_b200 import _native as N
+    from nanovllm_voxcpm_b200 import backbone as BB
+    from nanovllm_voxcpm_b200 import glue as G
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(0)
+    dev, dt = torch.device("cuda", 0), torch.bfloat16
+    T, H, I, heads, kvh, D = 8192, 1024, 4096, 16, 2, 64
+    peak, peak_kind = measured_peak()
+    reps, warm = max(args.steps, 20), max(args.warmup, 3)
+
+    def timed(fn, n_sets):
+        """us per call; one pass over all buffer sets is captured in a CUDA graph so that the host-side cost of
+        a call (tens of microseconds of Python) does not hide kernels that take about as long."""
+        stream = torch.cuda.Stream(dev)
+        with torch.cuda.stream(stream):
+            for i in range(max(warm, n_sets)):
+                fn(i % n_sets)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(n_sets):
+                    fn(i)
+            for _ in range(warm):
+                graph.replay()
+            stream.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e.record(stream)
+            e.synchronize()
+        return s.elapsed_time(e) / (reps * n_sets) * 1e3
+
+    out = {}
+    # residual add + RMSNorm: reads x, residual; writes hidden, normed
+    n = 6
+    xs = [torch.randn(T, H, device=dev).to(dt) for _ in range(n)]
+    rs = [torch.randn(T, H, device=dev).to(dt) for _ in range(n)]
+    hs, ns = [torch.empty_like(x) for x in xs], [torch.empty_like(x) for x in xs]
+    w = torch.ones(H, device=dev, dtype=dt)
+
+    def torch_norm(i):
+        h = rs[i] + xs[i]
+        BB._rms_norm(h, w, 1e-6)
+
+    nbytes = 4 * T * H * 2
+    us, ref_us = timed(lambda i: G.add_rms_norm(xs[i], rs[i], w, 1e-6, out=ns[i], hidden_out=hs[i]), n), timed(torch_norm, n)
+    out["add_rmsnorm"] = {"us": us, "gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak, "torch_ops_us": ref_us}
+    del xs, rs, hs, ns
+    # RoPE + cache store: reads q, k, v rows, writes q, k rows and the k, v cache rows
+    n = 10
+    width = (heads + 2 * kvh) * D
+    qkvs = [torch.randn(T, width, device=dev).to(dt) for _ in range(n)]
+    pos = torch.randint(0, 4096, (T,), device=dev)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    freqs = torch.outer(torch.arange(4096, dtype=torch.float32), inv)
+    cos, sin = freqs.cos().to(dev), freqs.sin().to(dev)
+    kc, vc = torch.zeros(T, kvh, D, device=dev, dtype=dt), torch.zeros(T, kvh, D, device=dev, dtype=dt)
+    slot = torch.randperm(T, device=dev)
+    slot32 = slot.to(torch.int32)
+
+    def torch_rope(i):
+        q, k, v = qkvs[i].split([heads * D, kvh * D, kvh * D], dim=-1)
+        c, s = cos[pos].unsqueeze(1), sin[pos].unsqueeze(1)
+        BB._rope(q.view(T, heads, D), c, s)
+        kk = BB._rope(k.view(T, kvh, D), c, s)
+        kc.index_copy_(0, slot, kk)
+        vc.index_copy_(0, slot, v.reshape(T, kvh, D))
+
+    nbytes = T * (width + (heads + kvh) * D + 2 * kvh * D) * 2
+    us = timed(lambda i: G.rope_kv_store(qkvs[i], heads, kvh, D, positions=pos, cos=cos, sin=sin, k_cache=kc, v_cache=vc,
+                                         slot_mapping=slot32), n)
+    out["rope_kv_store"] = {"us": us, "gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak, "torch_ops_us": timed(torch_rope, n)}
+    del qkvs
+    # SiLU * up: reads gate | up, writes the product
+    n = 2
+    gus = [torch.randn(T, 2 * I, device=dev).to(dt) for _ in range(n)]
+    outs = [torch.empty(T, I, device=dev, dtype=dt) for _ in range(n)]
+
+    def torch_silu(i):
+        g, u = gus[i].chunk(2, dim=-1)
+        torch.nn.functional.silu(g) * u
+
+    nbytes = 3 * T * I * 2
+    us = timed(lambda i: G.silu_and_mul(gus[i], out=outs[i]), n)
+    out["silu_mul"] = {"us": us, "gbs": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak, "torch_ops_us": timed(torch_silu, n)}
+    total = sum(v["us"] for v in out.values())
+    total_bytes = sum(v["gbs"] * v["us"] * 1e3 for v in out.values())
+    print(json.dumps({
+        "metric": "decoder-layer glue GB/s (residual add + RMSNorm, RoPE + cache store, SiLU * up; algorithmic bytes)",
+        "value": total_bytes / total / 1e3, "unit": "GB/s", "n_gpus": 1, "steps": reps, "warmup": warm,
+        "ms_per_step": total * 1e-3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"glue of one layer on {T} rows: hidden {H}, {heads}/{kvh} heads x {D}, intermediate {I}",
+                   "cache_defeat": "buffer sets rotated, larger than L2 together"},
+        "roofline": {"bound": "hbm", "achieved": total_bytes / total / 1e3, "peak": peak, "unit": "GB/s",
+                     "frac": total_bytes / total / 1e3 / peak, "traffic": None, "peak_kind": peak_kind},
+        "kernels": out, "gpu_launches": (6 + 10 + 2) * reps, "device_status": N.device_status(),
     }))
 
 
@@ -899,6 +1012,8 @@ def main():
         return run_tp_arm(args)
     if args.workload == "admission":
         return run_admission_arm(args)
+    if args.workload == "glue":
+        return run_glue_arm(args)
     if args.workload == "backbone" and args.impl in ("b200", "reference-gpu"):
         return run_backbone_arm(args)
     if args.impl == "reference":

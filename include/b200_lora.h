@@ -207,6 +207,39 @@ size_t lora_b200_static_scratch_bytes(void);
  */
 int lora_b200_load_slot(const void* staging, int32_t n_desc, int64_t max_elems, void* stream);
 
+/*
+ * Memory-bound glue of a decoder layer around the four projections (bf16 / fp16, rows 16-byte aligned,
+ * widths multiples of 8), one launch each, the row read once and written once.
+ *
+ * lora_b200_glue_add_rmsnorm: hidden = residual + x (rounded to dtype), normed = hidden * rsqrt(mean(hidden^2)
+ * + eps) * weight, statistics in fp32, one rounding of the result. residual NULL: plain rms_norm of x.
+ * hidden_out NULL: the sum is not stored; it may alias residual or x. norm_of_rounded_sum = 1: the norm
+ * reads the rounded sum (`hidden = residual + sublayer(...)` followed by `RMSNorm.rms_forward`,
+ * nanovllm_voxcpm/models/voxcpm2/model.py:291-297, layers/layernorm.py:18-22); 0: the fp32 sum
+ * (`RMSNorm.add_rms_forward`, layers/layernorm.py:24-32). hidden <= 4096.
+ *
+ * lora_b200_glue_rope_kv_store: qkv [T, (num_heads + 2 num_kv_heads) * head_dim] = q | k | v per row. Rotates
+ * every q and k head in place, y = x * cos[pos] + rotate_half(x) * sin[pos] with fp32 products and sum rounded
+ * separately (`apply_rotary_emb`, models/voxcpm2/model_utils_rope.py:50-63, called from
+ * `MiniCPMLongRoPE.forward`, models/voxcpm2/model.py:81-94), cos / sin tables [max_position, table_dim] of
+ * table_dtype with table_dim = head_dim (the reference's cache) or head_dim / 2, positions clamped to the
+ * table; then copies the rotated k row and the v row to k_cache / v_cache [slots, num_kv_heads * head_dim] at
+ * slot_mapping[t], skipping -1 (`store_kvcache`, layers/attention.py:10-49). positions / tables all NULL: no
+ * rotation (use_rope = False); caches NULL: no store.
+ *
+ * lora_b200_glue_silu_mul: out[t, j] = silu(gate_up[t, j]) * gate_up[t, intermediate + j] in fp32, one rounding
+ * (`SiluAndMul`, layers/activation.py:11-14).
+ */
+int lora_b200_glue_add_rmsnorm(void* normed, int64_t normed_ld, void* hidden_out, int64_t hidden_ld, const void* x,
+                               int64_t x_ld, const void* residual, int64_t residual_ld, const void* weight, int32_t T,
+                               int32_t hidden, float eps, int32_t norm_of_rounded_sum, int32_t dtype, void* stream);
+int lora_b200_glue_rope_kv_store(void* qkv, int64_t qkv_ld, int32_t T, int32_t num_heads, int32_t num_kv_heads,
+                                 int32_t head_dim, const int64_t* positions, const void* cos_table, const void* sin_table,
+                                 int32_t table_dim, int32_t table_dtype, int32_t max_position, void* k_cache, void* v_cache,
+                                 const int32_t* slot_mapping, int32_t dtype, void* stream);
+int lora_b200_glue_silu_mul(void* out, int64_t out_ld, const void* gate_up, int64_t gate_up_ld, int32_t T,
+                            int32_t intermediate, int32_t dtype, void* stream);
+
 /* conventions of lora_b200_build_metadata */
 #define B200_LORA_META_GRAPH 0  /* fixed buckets [-1, 0 .. S-1], bucket 0 always empty (CUDA-graph buffers) */
 #define B200_LORA_META_KERNEL 1 /* compact ids incl. the -1 bucket with its rows (LoRAKernelMeta.prepare_tensors) */

@@ -65,6 +65,15 @@ _SIGNATURES = {
         c_int32, [c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     ),
     "lora_b200_load_slot": (c_int32, [c_void_p, c_int32, c_int64, c_void_p]),
+    "lora_b200_glue_add_rmsnorm": (
+        c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int32, c_int32,
+                  c_float, c_int32, c_int32, c_void_p],
+    ),
+    "lora_b200_glue_rope_kv_store": (
+        c_int32, [c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
+                  c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_void_p],
+    ),
+    "lora_b200_glue_silu_mul": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32, c_void_p]),
     "lora_b200_tp_allreduce": (
         c_int32, [c_void_p, c_void_p, c_int32, POINTER(c_void_p), c_int32, c_int32, c_int32, c_void_p],
     ),

@@ -4,10 +4,11 @@ A MiniCPM-4 style pre-norm decoder with the structure of the reference's backbon
 (``nanovllm_voxcpm/models/voxcpm2/model.py:109-334``: ``Cpm4Attention`` = qkv projection -> RoPE ->
 paged attention -> o projection, ``Cpm4MLP`` = gate_up projection -> SiLU * up -> down projection,
 ``Cpm4DecoderLayer`` = RMSNorm + residual around both), random-init weights, input embeddings fed
-directly. The four projections are this package's LoRA layers; everything around them is library
-code and outside the path: RMSNorm / RoPE / SiLU in plain torch, attention and the paged KV cache
+directly. The four projections are this package's LoRA layers; attention and the paged KV cache go
 through flash_attn (``flash_attn_varlen_func`` for prefill, ``flash_attn_with_kvcache`` with a block
-table for decode), as in the reference (``layers/attention.py:10-79``).
+table for decode), as in the reference (``layers/attention.py:10-79``). The steps in between
+(residual add + RMSNorm, RoPE + cache store, SiLU * up) run as plain torch ops, or, with
+``Decoder.fused_glue = True``, as the single-launch kernels of ``glue.py``.
 
 It exists to time a whole step with the multi-LoRA kernels in their real surroundings (one prefill
 step over all prompts, then decode steps replayed from a CUDA graph) and to compare it with the same
@@ -22,6 +23,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import glue as G
 from . import layers as L
 from .batch_plan import GraphLoRABuffers, build_lora_batch_plan_from_token_to_slot, build_lora_context_from_batch_plan
 from .context import LoRAContext, reset_lora_context, set_lora_context
@@ -101,6 +103,22 @@ class DecoderAttention(nn.Module):
                                           block_table=step.block_tables, softmax_scale=scale, causal=True)
         return self.o_proj(out.reshape(-1, self.q_size))
 
+    def forward_fused(self, positions, normed, step: AttentionStep, cos, sin, slot_mapping_i32) -> torch.Tensor:
+        """Same as ``forward`` with RoPE and the cache store as one in-place kernel over the packed qkv rows."""
+        from flash_attn import flash_attn_varlen_func, flash_attn_with_kvcache
+
+        cfg = self.cfg
+        q, k, v = G.rope_kv_store(self.qkv_proj(normed), cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, positions=positions,
+                                  cos=cos, sin=sin, k_cache=self.k_cache, v_cache=self.v_cache, slot_mapping=slot_mapping_i32)
+        scale = cfg.head_dim ** -0.5
+        if step.is_prefill:
+            out = flash_attn_varlen_func(q, k, v, step.cu_seqlens, step.cu_seqlens, step.max_seqlen, step.max_seqlen,
+                                         softmax_scale=scale, causal=True)
+        else:
+            out = flash_attn_with_kvcache(q.unsqueeze(1), self.k_cache, self.v_cache, cache_seqlens=step.context_lens,
+                                          block_table=step.block_tables, softmax_scale=scale, causal=True)
+        return self.o_proj(out.reshape(-1, self.q_size))
+
 
 class DecoderMLP(nn.Module):
     def __init__(self, cfg: DecoderConfig):
@@ -143,7 +161,26 @@ class Decoder(nn.Module):
         self.register_buffer("cos", freqs.cos(), persistent=False)
         self.register_buffer("sin", freqs.sin(), persistent=False)
 
+    #: True: the steps between the projections run as this package's single-launch kernels (``glue.py``):
+    #: residual add + RMSNorm, RoPE + cache store, SiLU * up; False: plain torch ops
+    fused_glue = False
+
+    def _forward_fused(self, embeds, positions, step: AttentionStep):
+        eps = self.cfg.rms_norm_eps
+        slot_i32 = step.slot_mapping.to(torch.int32)
+        hidden = embeds
+        normed, _ = G.add_rms_norm(hidden, None, self.layers[0].input_layernorm, eps)
+        for i, layer in enumerate(self.layers):
+            attn = layer.self_attn.forward_fused(positions, normed, step, self.cos, self.sin, slot_i32)
+            normed, hidden = G.add_rms_norm(attn, hidden, layer.post_attention_layernorm, eps)
+            down = layer.mlp.down_proj(G.silu_and_mul(layer.mlp.gate_up_proj(normed)))
+            following = self.layers[i + 1].input_layernorm if i + 1 < len(self.layers) else self.norm
+            normed, hidden = G.add_rms_norm(down, hidden, following, eps)
+        return normed
+
     def forward(self, embeds, positions, step: AttentionStep):
+        if self.fused_glue:
+            return self._forward_fused(embeds, positions, step)
         cos_sin = (self.cos[positions].unsqueeze(1), self.sin[positions].unsqueeze(1))
         hidden = embeds
         for layer in self.layers:

@@ -7,6 +7,7 @@
 #include "metadata.cuh"
 #include "tp_exchange.cuh"
 #include "slot_loader.cuh"
+#include "glue.cuh"
 #include "sgmv_tc.cuh"
 #include "gemm_tc.cuh"
 
@@ -125,6 +126,31 @@ int lora_b200_build_metadata(const int32_t* token_to_slot, int32_t T, int32_t S,
 
 int lora_b200_load_slot(const void* staging, int32_t n_desc, int64_t max_elems, void* stream) {
   return slot_load_launch(staging, n_desc, max_elems, static_cast<cudaStream_t>(stream));
+}
+
+int lora_b200_glue_add_rmsnorm(void* normed, int64_t normed_ld, void* hidden_out, int64_t hidden_ld, const void* x,
+                               int64_t x_ld, const void* residual, int64_t residual_ld, const void* weight, int32_t T,
+                               int32_t hidden, float eps, int32_t norm_of_rounded_sum, int32_t dtype, void* stream) {
+  return add_rmsnorm_launch(normed, normed_ld, hidden_out, hidden_ld, x, x_ld, residual, residual_ld, weight, T, hidden, eps,
+                            norm_of_rounded_sum, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int lora_b200_glue_rope_kv_store(void* qkv, int64_t qkv_ld, int32_t T, int32_t num_heads, int32_t num_kv_heads,
+                                 int32_t head_dim, const int64_t* positions, const void* cos_table, const void* sin_table,
+                                 int32_t table_dim, int32_t table_dtype, int32_t max_position, void* k_cache, void* v_cache,
+                                 const int32_t* slot_mapping, int32_t dtype, void* stream) {
+  RopeKvParams p;
+  p.qkv = qkv; p.qkv_ld = qkv_ld; p.T = T; p.Hq = num_heads; p.Hk = num_kv_heads; p.D = head_dim;
+  p.positions = positions; p.cos = cos_table; p.sin = sin_table;
+  p.table_dim = table_dim; p.table_dtype = table_dtype; p.max_pos = max_position;
+  p.k_cache = k_cache; p.v_cache = v_cache; p.slot_mapping = slot_mapping;
+  p.apply_rope = (cos_table != nullptr || sin_table != nullptr || positions != nullptr) ? 1 : 0;
+  return rope_kv_store_launch(p, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int lora_b200_glue_silu_mul(void* out, int64_t out_ld, const void* gate_up, int64_t gate_up_ld, int32_t T,
+                            int32_t intermediate, int32_t dtype, void* stream) {
+  return silu_mul_launch(out, out_ld, gate_up, gate_up_ld, T, intermediate, dtype, static_cast<cudaStream_t>(stream));
 }
 
 size_t lora_b200_tp_exchange_bytes(int32_t tp, int32_t capacity) { return tp_exchange_bytes(tp, capacity); }

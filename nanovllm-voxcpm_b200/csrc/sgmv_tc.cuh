@@ -21,7 +21,7 @@ constexpr int kSgmvThreads = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, wa
 constexpr int kSgmvBM = 128;        // rows per block / MMA M
 constexpr int kSgmvBK = 64;         // K columns per shrink stage (one 128-byte swizzle row)
 constexpr int kSgmvBN = 256;        // output columns per expand tile
-constexpr int kSgmvShrinkStages = 4;
+constexpr int kSgmvShrinkMaxStages = 8;  // the launch picks as many 64-column stages as fit into shared memory
 constexpr int kSgmvExpandStages = 3;
 constexpr int kSgmvAutoMinTokens = 512;  // IMPL_AUTO uses these kernels from this batch size on
 
@@ -34,6 +34,7 @@ struct SgmvArgs {
   const float* scale_per_slot; float scaling;
   int zero_fill;                            // shrink: write zero rows for tokens without adapter
   int skip_clean;                           // expand: leave blocks in which every row has an adapter to tc_tile_kernel
+  int shrink_stages;                        // shrink: depth of the TMA ring (set by the launch)
 };
 
 struct SgmvMaps {
@@ -93,27 +94,27 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ int s_slot[kSgmvBM], run_slot[kSgmvBM], run_lo[kSgmvBM], run_hi[kSgmvBM];
   __shared__ int nruns_s;
-  __shared__ __align__(8) uint64_t bars[2 * kSgmvShrinkStages + 2];
+  __shared__ __align__(8) uint64_t bars[2 * kSgmvShrinkMaxStages + 2];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int blk = blockIdx.x;
-  const int r = a.r_max, n = a.n;
+  const int r = a.r_max, n = a.n, NS = a.shrink_stages;
   const uint32_t a_tile_bytes = (uint32_t)r * kSgmvBK * 2;
   const uint32_t x_tile_bytes = kSgmvBM * kSgmvBK * 2;
   const uint32_t stage_bytes = x_tile_bytes + (uint32_t)n * a_tile_bytes;
   const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * (uint32_t)s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (uint32_t)(kSgmvShrinkStages + s); };
-  const uint32_t acc_full = bar0 + 8u * (2 * kSgmvShrinkStages);
+  auto empty_bar = [&](int s) { return bar0 + 8u * (uint32_t)(kSgmvShrinkMaxStages + s); };
+  const uint32_t acc_full = bar0 + 8u * (2 * kSgmvShrinkMaxStages);
   const uint32_t acc_empty = acc_full + 8u;
   int tmem_cols = 32;  // the last slice is read in 32-column chunks
   while (tmem_cols < (n - 1) * r + ((r + 31) & ~31)) tmem_cols *= 2;
 
   if (tid == 0) {
-    for (int s = 0; s < kSgmvShrinkStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < NS; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 128);
     abort_flag = 0;
@@ -143,7 +144,7 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
           tma_load_2d(base, &maps.x, kc * kSgmvBK, blk * kSgmvBM, full_bar(st));
           for (int s = 0; s < n; ++s)
             tma_load_2d(base + x_tile_bytes + (uint32_t)s * a_tile_bytes, &maps.a[s], kc * kSgmvBK, slot * r, full_bar(st));
-          if (++st == kSgmvShrinkStages) { st = 0; ++round; }
+          if (++st == NS) { st = 0; ++round; }
         }
       }
     }
@@ -166,7 +167,7 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
               umma_bf16(tmem_base + (uint32_t)(s * r), xdesc + 2u * k4, adesc + 2u * k4, idesc, (kc > 0 || k4 > 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(st));  // stage reusable once these MMAs have read it
-          if (++st == kSgmvShrinkStages) { st = 0; ++round; }
+          if (++st == NS) { st = 0; ++round; }
         }
         umma_commit(acc_full);
       }
@@ -414,8 +415,12 @@ inline int sgmv_set_smem(const void* kernel, size_t bytes) {
   return B200_LORA_OK;
 }
 
-inline int sgmv_launch_shrink(const SgmvMaps& maps, const SgmvArgs& a, cudaStream_t stream) {
-  const size_t smem = (size_t)kSgmvShrinkStages * (kSgmvBM * kSgmvBK * 2 + (size_t)a.n * a.r_max * kSgmvBK * 2) + 1024;
+inline int sgmv_launch_shrink(const SgmvMaps& maps, const SgmvArgs& a_in, cudaStream_t stream) {
+  SgmvArgs a = a_in;
+  // one CTA per SM streams its 128 rows of x: the deeper the ring, the more bytes are in flight per SM
+  const size_t stage = kSgmvBM * kSgmvBK * 2 + (size_t)a.n * a.r_max * kSgmvBK * 2;
+  a.shrink_stages = (int)std::min<size_t>(kSgmvShrinkMaxStages, std::max<size_t>(2, (size_t)(216 * 1024) / stage));
+  const size_t smem = (size_t)a.shrink_stages * stage + 1024;
   if (int rc = sgmv_set_smem(reinterpret_cast<const void*>(sgmv_shrink_kernel), smem)) return rc;
   const int nblk = (a.T + kSgmvBM - 1) / kSgmvBM;
   sgmv_shrink_kernel<<<nblk, kSgmvThreads, smem, stream>>>(maps, a);

@@ -66,3 +66,32 @@ def test_backbone_prefill_and_decode_match_the_oracle_backend():
     torch.testing.assert_close(out_graph, ref_decode, atol=6e-2, rtol=6e-2)
     # the request without adapter sees exactly the base model in prefill (rows 217..480 of the single chunk)
     assert torch.equal(out_prefill[217:481], out_base[217:481])
+
+
+def test_fused_glue_step_matches_the_torch_glue_step():
+    """The same decoder with residual add + RMSNorm, RoPE + cache store and SiLU * up as single launches: outputs
+    within the rounding of a two-layer bf16 stack, KV caches equal, graph replay equal to eager launches."""
+    model, work = _model_and_work()
+    plain = BB.BackboneRunner(model, work, use_lora=True)
+    plain.prefill()
+    plain_prefill = plain.last_output.float().cpu()
+    plain_k = model.layers[0].self_attn.k_cache.clone()
+    plain.decode(3, use_graph=False)
+    plain_decode = plain.last_output.float().cpu()
+    try:
+        model.fused_glue = True
+        fused = BB.BackboneRunner(model, work, use_lora=True)  # allocates fresh caches
+        fused.prefill()
+        fused_prefill = fused.last_output.float().cpu()
+        # layer 0's cache holds the rotated k of the first projection: same inputs up to the norm's last place
+        torch.testing.assert_close(model.layers[0].self_attn.k_cache.float(), plain_k.float(), atol=2e-2, rtol=2e-2)
+        fused.decode(3, use_graph=True)
+        fused_graph = fused.last_output.float().cpu()
+        eager = BB.BackboneRunner(model, work, use_lora=True)
+        eager.prefill()
+        eager.decode(3, use_graph=False)
+        assert torch.equal(fused_graph, eager.last_output.float().cpu())
+    finally:
+        model.fused_glue = False
+    torch.testing.assert_close(fused_prefill, plain_prefill, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(fused_graph, plain_decode, atol=3e-2, rtol=3e-2)
