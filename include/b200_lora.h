@@ -225,7 +225,7 @@ int lora_b200_load_slot(const void* staging, int32_t n_desc, int64_t max_elems, 
  * table_dtype with table_dim = head_dim (the reference's cache) or head_dim / 2, positions clamped to the
  * table; then copies the rotated k row and the v row to k_cache / v_cache [slots, num_kv_heads * head_dim] at
  * slot_mapping[t], skipping -1 (`store_kvcache`, layers/attention.py:10-49). positions / tables all NULL: no
- * rotation (use_rope = False); caches NULL: no store.
+ * rotation (use_rope = False); caches NULL: no store. head_dim must be a multiple of 16.
  *
  * lora_b200_glue_silu_mul: out[t, j] = silu(gate_up[t, j]) * gate_up[t, intermediate + j] in fp32, one rounding
  * (`SiluAndMul`, layers/activation.py:11-14).

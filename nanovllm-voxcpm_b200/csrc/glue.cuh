@@ -135,57 +135,60 @@ __device__ __forceinline__ float table_at(const void* tab, int dtype, int64_t id
   return __half2float(static_cast<const __half*>(tab)[idx]);
 }
 
-// One CTA per token. Rotation items: (head, pair of adjacent columns j, j+1 in the first half) ->
-// y[j] = x[j] * cos[j] - x[j + D/2] * sin[j], y[j + D/2] = x[j + D/2] * cos[j + D/2] + x[j] * sin[j + D/2], each
-// product and the sum rounded separately in fp32 as the reference's elementwise chain does. The rotated k
-// row and the v row then go to the cache (16-byte copies).
+// Work items of 16 bytes, flat over (token, item): a rotation item is (head, 8 adjacent columns j..j+7 of the
+// first half) -> y[j] = x[j] * cos[j] - x[j + D/2] * sin[j], y[j + D/2] = x[j + D/2] * cos[j + D/2] + x[j] * sin[j + D/2],
+// each product and the sum rounded separately in fp32 as the reference's elementwise chain does; a rotated k
+// vector also goes to the cache. The remaining items of a token copy its v row (and its k row when nothing is
+// rotated) to the cache.
+constexpr int kRopeThreads = 256;
+
 template <typename T>
-__global__ void __launch_bounds__(128) rope_kv_store_kernel(const RopeKvParams p) {
-  const int tok = blockIdx.x;
-  T* row = static_cast<T*>(p.qkv) + (int64_t)tok * p.qkv_ld;
-  const int half = p.D >> 1, pairs = half >> 1;
-  const int q_size = p.Hq * p.D, kv_size = p.Hk * p.D;
-  const int64_t slot = (p.k_cache != nullptr && p.slot_mapping != nullptr) ? (int64_t)p.slot_mapping[tok] : -1;
-  T* kc = slot >= 0 ? static_cast<T*>(p.k_cache) + slot * kv_size : nullptr;
-  T* vc = slot >= 0 ? static_cast<T*>(p.v_cache) + slot * kv_size : nullptr;
-  if (p.apply_rope) {
-    int64_t pos = p.positions[tok];
-    pos = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
-    const int64_t tb = pos * p.table_dim;
-    const int hi_off = p.table_dim == p.D ? half : 0;
-    const int items = (p.Hq + p.Hk) * pairs;
-    for (int it = threadIdx.x; it < items; it += blockDim.x) {
-      const int head = it / pairs, j = (it - head * pairs) * 2;
+__global__ void __launch_bounds__(kRopeThreads) rope_kv_store_kernel(const RopeKvParams p) {
+  const int half = p.D >> 1, vec_per_half = half >> 3;
+  const int q_size = p.Hq * p.D, kv_size = p.Hk * p.D, kv_vecs = kv_size >> 3;
+  const int rot_items = p.apply_rope ? (p.Hq + p.Hk) * vec_per_half : 0;
+  const bool store = p.k_cache != nullptr && p.slot_mapping != nullptr;
+  const int copy_items = store ? (p.apply_rope ? kv_vecs : 2 * kv_vecs) : 0;
+  const int per_tok = rot_items + copy_items;
+  const int64_t total = (int64_t)p.T * per_tok;
+  const int hi_off = p.table_dim == p.D ? half : 0;
+  for (int64_t idx = (int64_t)blockIdx.x * kRopeThreads + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * kRopeThreads) {
+    const int tok = (int)(idx / per_tok), it = (int)(idx - (int64_t)tok * per_tok);
+    T* row = static_cast<T*>(p.qkv) + (int64_t)tok * p.qkv_ld;
+    const int64_t slot = store ? (int64_t)p.slot_mapping[tok] : -1;
+    if (it < rot_items) {
+      const int head = it / vec_per_half, j = (it - head * vec_per_half) * 8;
       T* h = row + head * p.D;  // k heads follow the q heads directly
-      const float2 lo = make_float2(to_float<T>(h[j]), to_float<T>(h[j + 1]));
-      const float2 hi = make_float2(to_float<T>(h[half + j]), to_float<T>(h[half + j + 1]));
-      float out_lo[2], out_hi[2];
+      int64_t pos = p.positions[tok];
+      pos = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
+      const int64_t tb = pos * p.table_dim + j;
+      Vec8<T> lo, hi, olo, ohi;
+      lo.raw = *reinterpret_cast<const uint4*>(h + j);
+      hi.raw = *reinterpret_cast<const uint4*>(h + half + j);
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const float x1 = e ? lo.y : lo.x, x2 = e ? hi.y : hi.x;
-        const float c1 = table_at(p.cos, p.table_dtype, tb + j + e), s1 = table_at(p.sin, p.table_dtype, tb + j + e);
-        const float c2 = table_at(p.cos, p.table_dtype, tb + hi_off + j + e);
-        const float s2 = table_at(p.sin, p.table_dtype, tb + hi_off + j + e);
-        out_lo[e] = __fadd_rn(__fmul_rn(x1, c1), __fmul_rn(-x2, s1));
-        out_hi[e] = __fadd_rn(__fmul_rn(x2, c2), __fmul_rn(x1, s2));
+      for (int e = 0; e < 8; ++e) {
+        const float x1 = lo.get(e), x2 = hi.get(e);
+        const float c1 = table_at(p.cos, p.table_dtype, tb + e), s1 = table_at(p.sin, p.table_dtype, tb + e);
+        const float c2 = hi_off ? table_at(p.cos, p.table_dtype, tb + hi_off + e) : c1;
+        const float s2 = hi_off ? table_at(p.sin, p.table_dtype, tb + hi_off + e) : s1;
+        olo.set(e, __fadd_rn(__fmul_rn(x1, c1), __fmul_rn(-x2, s1)));
+        ohi.set(e, __fadd_rn(__fmul_rn(x2, c2), __fmul_rn(x1, s2)));
       }
-      const T l0 = from_float<T>(out_lo[0]), l1 = from_float<T>(out_lo[1]);
-      const T h0 = from_float<T>(out_hi[0]), h1 = from_float<T>(out_hi[1]);
-      h[j] = l0; h[j + 1] = l1; h[half + j] = h0; h[half + j + 1] = h1;
-      if (kc != nullptr && head >= p.Hq) {
-        T* d = kc + (head - p.Hq) * p.D;
-        d[j] = l0; d[j + 1] = l1; d[half + j] = h0; d[half + j + 1] = h1;
+      *reinterpret_cast<uint4*>(h + j) = olo.raw;
+      *reinterpret_cast<uint4*>(h + half + j) = ohi.raw;
+      if (slot >= 0 && head >= p.Hq) {
+        T* d = static_cast<T*>(p.k_cache) + slot * kv_size + (head - p.Hq) * p.D;
+        *reinterpret_cast<uint4*>(d + j) = olo.raw;
+        *reinterpret_cast<uint4*>(d + half + j) = ohi.raw;
       }
+    } else if (slot >= 0) {
+      int c = it - rot_items;  // v vectors first, then (no rotation) the k vectors
+      const bool is_v = c < kv_vecs;
+      if (!is_v) c -= kv_vecs;
+      const T* src = row + q_size + (is_v ? kv_size : 0) + 8 * c;
+      T* dst = static_cast<T*>(is_v ? p.v_cache : p.k_cache) + slot * kv_size + 8 * c;
+      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
     }
-  } else if (kc != nullptr) {
-    const uint4* src = reinterpret_cast<const uint4*>(row + q_size);
-    uint4* dst = reinterpret_cast<uint4*>(kc);
-    for (int i = threadIdx.x; i < kv_size / 8; i += blockDim.x) dst[i] = src[i];
-  }
-  if (vc != nullptr) {
-    const uint4* src = reinterpret_cast<const uint4*>(row + q_size + kv_size);
-    uint4* dst = reinterpret_cast<uint4*>(vc);
-    for (int i = threadIdx.x; i < kv_size / 8; i += blockDim.x) dst[i] = src[i];
   }
 }
 
@@ -195,9 +198,10 @@ inline int rope_kv_store_launch(const RopeKvParams& p, int dtype, cudaStream_t s
   if (p.qkv == nullptr) return fail(B200_LORA_EINVAL, "rope_kv_store: null qkv");
   if (dtype != B200_LORA_BF16 && dtype != B200_LORA_F16)
     return fail(B200_LORA_EUNSUPPORTED, "rope_kv_store: bf16 and fp16 only");
-  if (p.D % 8 != 0 || p.qkv_ld % 8 != 0 || !aligned16(p.qkv) || !aligned16(p.k_cache) || !aligned16(p.v_cache))
-    return fail(B200_LORA_EUNSUPPORTED, "rope_kv_store: head_dim and the row pitch must be multiples of 8 elements, "
-                                        "rows 16-byte aligned");
+  if (p.D % 16 != 0 || p.qkv_ld % 8 != 0 || !aligned16(p.qkv) || !aligned16(p.k_cache) || !aligned16(p.v_cache) ||
+      !aligned16(p.cos) || !aligned16(p.sin))
+    return fail(B200_LORA_EUNSUPPORTED, "rope_kv_store: head_dim must be a multiple of 16 and the row pitch of 8 elements, "
+                                        "rows and tables 16-byte aligned");
   if ((p.k_cache == nullptr) != (p.v_cache == nullptr)) return fail(B200_LORA_EINVAL, "rope_kv_store: one cache is null");
   if (p.apply_rope) {
     if (p.positions == nullptr || p.cos == nullptr || p.sin == nullptr || p.max_pos <= 0)
@@ -207,8 +211,13 @@ inline int rope_kv_store_launch(const RopeKvParams& p, int dtype, cudaStream_t s
     if (p.table_dtype != B200_LORA_F32 && p.table_dtype != B200_LORA_BF16 && p.table_dtype != B200_LORA_F16)
       return fail(B200_LORA_EINVAL, "rope_kv_store: bad table dtype");
   }
-  if (dtype == B200_LORA_BF16) rope_kv_store_kernel<__nv_bfloat16><<<(unsigned)p.T, 128, 0, stream>>>(p);
-  else rope_kv_store_kernel<__half><<<(unsigned)p.T, 128, 0, stream>>>(p);
+  const bool store = p.k_cache != nullptr && p.slot_mapping != nullptr;
+  const int per_tok = (p.apply_rope ? (p.Hq + p.Hk) * (p.D / 16) : 0) + (store ? (p.apply_rope ? 1 : 2) * p.Hk * p.D / 8 : 0);
+  if (per_tok == 0) return B200_LORA_OK;
+  const int64_t want = ((int64_t)p.T * per_tok + kRopeThreads - 1) / kRopeThreads;
+  const unsigned grid = (unsigned)std::min<int64_t>(want, 148 * 16);
+  if (dtype == B200_LORA_BF16) rope_kv_store_kernel<__nv_bfloat16><<<grid, kRopeThreads, 0, stream>>>(p);
+  else rope_kv_store_kernel<__half><<<grid, kRopeThreads, 0, stream>>>(p);
   return check_launch("rope_kv_store_kernel");
 }
 
