@@ -63,6 +63,12 @@ def parse_args():
     ap.add_argument("--glue", default="fused", choices=["fused", "torch"],
                     help="backbone workload: the steps between the projections as this library's single-launch kernels "
                          "(residual add + RMSNorm, RoPE + cache store, SiLU * up) or as plain torch ops")
+    ap.add_argument("--prefetch", default="off", choices=["on", "off"],
+                    help="backbone workload: request the next layer's adapter weights into L2 from a side stream during "
+                         "decode steps")
+    ap.add_argument("--lora-order", default="first", choices=["first", "after"],
+                    help="backbone workload, decode steps: multi-LoRA delta written before the base GEMM, which then "
+                         "accumulates into it (first), or added after the GEMM as the reference does (after)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "linear", "backbone", "tp", "admission", "glue"],
@@ -704,6 +710,10 @@ def run_backbone_arm(args):
     model.init_random_(0)
     model.fill_adapter_slots_(cfg.max_loras, cfg.max_lora_rank, seed=1)
     model.fused_glue = args.glue == "fused" and args.impl == "b200"
+    model.prefetch_adapters = model.fused_glue and args.prefetch == "on"
+    from nanovllm_voxcpm_b200 import layers as L_
+
+    L_.LORA_FIRST = args.lora_order == "first" and args.impl == "b200"
     backend_name = "B200LoRABackend"
     if args.impl == "reference-gpu":
         # same decoder, same layers, but every LoRA call goes to the unmodified reference's own GPU backend
@@ -743,7 +753,8 @@ def run_backbone_arm(args):
         "adapter_overhead": {"decode": base["decode_tokens_per_s"] / lora["decode_tokens_per_s"],
                              "prefill": base["prefill_tokens_per_s"] / lora["prefill_tokens_per_s"]},
         "device_status": N.device_status(), "impl": args.impl, "lora_backend": backend_name,
-        "glue": "fused kernels" if model.fused_glue else "torch ops",
+        "glue": "fused kernels" if model.fused_glue else "torch ops", "adapter_prefetch": bool(model.prefetch_adapters),
+        "lora_order": "first" if L_.LORA_FIRST else "after",
     }))
 
 

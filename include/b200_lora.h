@@ -103,6 +103,25 @@ int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T,
                   void* stream);
 
 /*
+ * delta[t, cols] = scaling * scale_per_slot[slot_t] * (x[t] . A_s[slot_t]^T) . B_s[slot_t]^T for rows with an
+ * adapter, and -0.0 (sign bit only) over the slices' columns of every other row; delta is written, never read.
+ * Arguments as lora_b200_add. For a caller that runs the LoRA part BEFORE the base GEMM and lets the GEMM
+ * accumulate into the same buffer (beta = 1): x + (-0.0) == x, so rows without adapter end up bit-identical to
+ * the plain base result, and the launch no longer waits for the GEMM (under programmatic dependent launch its
+ * weight fetch overlaps whatever kernel of the caller runs before it). Decode batches take the fused kernel in
+ * overwrite mode; other shapes fill with -0.0 and add. No counterpart in the reference, which always adds after
+ * the base GEMM (nanovllm_voxcpm/layers/lora.py:341-366).
+ */
+int lora_b200_delta(void* delta, int64_t delta_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
+                    int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
+                    const int32_t* out_sizes, const int32_t* col_offsets, int32_t S, int32_t r_max,
+                    const int32_t* rank_per_slot, const float* scale_per_slot,
+                    const int32_t* token_to_slot, const int32_t* sorted_idx, const int32_t* slot_ids,
+                    const int32_t* counts, const int32_t* offsets, int32_t n_buckets, float scaling,
+                    int32_t dtype, int32_t impl, void* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/*
  * y = x . W^T (+ bias) + LoRA delta in one pass over y: the base GEMM runs on the tensor cores
  * and, for every 128-row block whose rows use one adapter slot, the delta tmp . B^T is
  * accumulated into the same TMEM accumulator before the single store of y (blocks with mixed
@@ -239,6 +258,17 @@ int lora_b200_glue_rope_kv_store(void* qkv, int64_t qkv_ld, int32_t T, int32_t n
                                  const int32_t* slot_mapping, int32_t dtype, void* stream);
 int lora_b200_glue_silu_mul(void* out, int64_t out_ld, const void* gate_up, int64_t gate_up_ld, int32_t T,
                             int32_t intermediate, int32_t dtype, void* stream);
+
+/*
+ * L2 prefetch hint for the adapter weights of the buckets of a step: for every bucket g with slot_ids[g] in
+ * [0, S) (and counts[g] > 0 when counts is given) and every slab j, asks for bytes_per_slot[j] bytes at
+ * slabs[j] + slot * slot_stride_bytes[j]. At most 16 slabs per call, 16-byte aligned. Nothing is written and
+ * nothing needs to be waited for; meant for a side stream, one layer ahead of the launches that read the slabs
+ * (no counterpart in the reference, whose kernels fetch their weights on the critical path of the step).
+ */
+int lora_b200_prefetch_slabs(const void* const* slabs, const int64_t* slot_stride_bytes, const int64_t* bytes_per_slot,
+                             int32_t n_slabs, const int32_t* slot_ids, const int32_t* counts, int32_t n_buckets, int32_t S,
+                             void* stream);
 
 /* conventions of lora_b200_build_metadata */
 #define B200_LORA_META_GRAPH 0  /* fixed buckets [-1, 0 .. S-1], bucket 0 always empty (CUDA-graph buffers) */

@@ -38,6 +38,12 @@ _SIGNATURES = {
          POINTER(c_int32), POINTER(c_int32), c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
          c_void_p, c_void_p, c_int32, c_float, c_int32, c_int32, c_void_p, c_size_t, c_void_p],
     ),
+    "lora_b200_delta": (
+        c_int32,
+        [c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32, POINTER(c_void_p), POINTER(c_void_p),
+         POINTER(c_int32), POINTER(c_int32), c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_int32, c_float, c_int32, c_int32, c_void_p, c_size_t, c_void_p],
+    ),
     "lora_b200_shrink": (
         c_int32,
         [c_void_p, c_int32, c_void_p, c_int64, c_int32, c_int32, c_int32, POINTER(c_void_p), c_int32, c_int32,
@@ -74,6 +80,9 @@ _SIGNATURES = {
                   c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_void_p],
     ),
     "lora_b200_glue_silu_mul": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32, c_void_p]),
+    "lora_b200_prefetch_slabs": (
+        c_int32, [POINTER(c_void_p), POINTER(c_int64), POINTER(c_int64), c_int32, c_void_p, c_void_p, c_int32, c_int32, c_void_p],
+    ),
     "lora_b200_tp_allreduce": (
         c_int32, [c_void_p, c_void_p, c_int32, POINTER(c_void_p), c_int32, c_int32, c_int32, c_void_p],
     ),

@@ -8,6 +8,7 @@
 #include "tp_exchange.cuh"
 #include "slot_loader.cuh"
 #include "glue.cuh"
+#include "prefetch.cuh"
 #include "sgmv_tc.cuh"
 #include "gemm_tc.cuh"
 
@@ -40,6 +41,20 @@ int fill_slices(SliceTable& st, int n_slices, const void* const* a_slabs,
     }
   }
   return B200_LORA_OK;
+}
+
+// y[row, slice columns] = -0.0 (sign bit only) for every slice; elem = bytes per element
+__global__ void fill_neg_zero_kernel(void* y, int64_t y_ld, const SliceTable st, int elem) {
+  const int64_t row = blockIdx.x;
+  for (int s = 0; s < st.n; ++s) {
+    if (elem == 2) {
+      uint16_t* dst = static_cast<uint16_t*>(y) + row * y_ld + st.col[s];
+      for (int i = threadIdx.x; i < st.out[s]; i += blockDim.x) dst[i] = 0x8000u;
+    } else {
+      uint32_t* dst = static_cast<uint32_t*>(y) + row * y_ld + st.col[s];
+      for (int i = threadIdx.x; i < st.out[s]; i += blockDim.x) dst[i] = 0x80000000u;
+    }
+  }
 }
 
 bool valid_dtype(int d) { return d == B200_LORA_BF16 || d == B200_LORA_F16 || d == B200_LORA_F32; }
@@ -151,6 +166,13 @@ int lora_b200_glue_rope_kv_store(void* qkv, int64_t qkv_ld, int32_t T, int32_t n
 int lora_b200_glue_silu_mul(void* out, int64_t out_ld, const void* gate_up, int64_t gate_up_ld, int32_t T,
                             int32_t intermediate, int32_t dtype, void* stream) {
   return silu_mul_launch(out, out_ld, gate_up, gate_up_ld, T, intermediate, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int lora_b200_prefetch_slabs(const void* const* slabs, const int64_t* slot_stride_bytes, const int64_t* bytes_per_slot,
+                             int32_t n_slabs, const int32_t* slot_ids, const int32_t* counts, int32_t n_buckets, int32_t S,
+                             void* stream) {
+  return prefetch_slabs_launch(slabs, slot_stride_bytes, bytes_per_slot, n_slabs, slot_ids, counts, n_buckets, S,
+                               static_cast<cudaStream_t>(stream));
 }
 
 size_t lora_b200_tp_exchange_bytes(int32_t tp, int32_t capacity) { return tp_exchange_bytes(tp, capacity); }
@@ -278,14 +300,15 @@ int lora_b200_shrink_allreduce_expand(void* y, int64_t y_ld, const void* x, int6
   return launch_generic_expand<float, float>(y, y_ld, tmp, T, st, S, r_max, token_to_slot, 1, st_);
 }
 
-int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
-                  int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
-                  const int32_t* out_sizes, const int32_t* col_offsets, int32_t S, int32_t r_max,
-                  const int32_t* rank_per_slot, const float* scale_per_slot,
-                  const int32_t* token_to_slot, const int32_t* sorted_idx, const int32_t* slot_ids,
-                  const int32_t* counts, const int32_t* offsets, int32_t n_buckets, float scaling,
-                  int32_t dtype, int32_t impl, void* workspace, size_t workspace_bytes,
-                  void* stream) {
+// overwrite = 0: y += delta (lora_b200_add); 1: y = delta, -0.0 in rows without one (lora_b200_delta)
+static int add_or_delta(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
+                        int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
+                        const int32_t* out_sizes, const int32_t* col_offsets, int32_t S, int32_t r_max,
+                        const int32_t* rank_per_slot, const float* scale_per_slot,
+                        const int32_t* token_to_slot, const int32_t* sorted_idx, const int32_t* slot_ids,
+                        const int32_t* counts, const int32_t* offsets, int32_t n_buckets, float scaling,
+                        int32_t dtype, int32_t impl, void* workspace, size_t workspace_bytes,
+                        void* stream, int overwrite) {
   if (!valid_dtype(dtype)) return fail(B200_LORA_EINVAL, "unknown dtype %d", dtype);
   if (T < 0 || in_dim < 1 || S < 1 || r_max < 1)
     return fail(B200_LORA_EINVAL, "bad sizes T=%d in=%d S=%d r_max=%d", T, in_dim, S, r_max);
@@ -318,6 +341,21 @@ int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T,
   SgmvProblem sp;
   sp.y = y; sp.y_ld = y_ld; sp.x = x; sp.x_ld = x_ld; sp.T = T; sp.in_dim = in_dim; sp.S = S; sp.r_max = r_max;
   sp.st = st; sp.scale_per_slot = scale_per_slot; sp.token_to_slot = token_to_slot; sp.scaling = scaling;
+
+  if (overwrite) {
+    // decode batches: the row-split kernel writes the delta (and the -0.0 rows) itself; everything else
+    // fills y with -0.0 first and then adds as usual (-0.0 + d == d)
+    bp.mode = 3;
+    bp.token_to_slot = token_to_slot;
+    const bool decode_like = T < kSgmvAutoMinTokens || T < 32 * n_buckets;
+    if (dtype == B200_LORA_BF16 && have_buckets && g_decode_kernel != 2 &&
+        (impl == B200_LORA_IMPL_BGMV || (impl == B200_LORA_IMPL_AUTO && decode_like)) && bgmv_supported(bp, nullptr))
+      return bgmv_launch(bp, st_);
+    bp.mode = 0;
+    bp.token_to_slot = nullptr;
+    fill_neg_zero_kernel<<<(unsigned)T, 128, 0, st_>>>(y, y_ld, st, dtype == B200_LORA_F32 ? 4 : 2);
+    if (int rc = check_launch("fill_neg_zero_kernel")) return rc;
+  }
 
   if (impl == B200_LORA_IMPL_AUTO) {
     // Long batches (prefill) go to the tensor-core kernels when scratch memory was supplied, decode
@@ -370,6 +408,32 @@ int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T,
     default:
       return fail(B200_LORA_EUNSUPPORTED, "impl %d is not available", impl);
   }
+}
+
+int lora_b200_add(void* y, int64_t y_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
+                  int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
+                  const int32_t* out_sizes, const int32_t* col_offsets, int32_t S, int32_t r_max,
+                  const int32_t* rank_per_slot, const float* scale_per_slot,
+                  const int32_t* token_to_slot, const int32_t* sorted_idx, const int32_t* slot_ids,
+                  const int32_t* counts, const int32_t* offsets, int32_t n_buckets, float scaling,
+                  int32_t dtype, int32_t impl, void* workspace, size_t workspace_bytes,
+                  void* stream) {
+  return add_or_delta(y, y_ld, x, x_ld, T, in_dim, n_slices, a_slabs, b_slabs, out_sizes, col_offsets, S, r_max,
+                      rank_per_slot, scale_per_slot, token_to_slot, sorted_idx, slot_ids, counts, offsets, n_buckets,
+                      scaling, dtype, impl, workspace, workspace_bytes, stream, 0);
+}
+
+int lora_b200_delta(void* delta, int64_t delta_ld, const void* x, int64_t x_ld, int32_t T, int32_t in_dim,
+                    int32_t n_slices, const void* const* a_slabs, const void* const* b_slabs,
+                    const int32_t* out_sizes, const int32_t* col_offsets, int32_t S, int32_t r_max,
+                    const int32_t* rank_per_slot, const float* scale_per_slot,
+                    const int32_t* token_to_slot, const int32_t* sorted_idx, const int32_t* slot_ids,
+                    const int32_t* counts, const int32_t* offsets, int32_t n_buckets, float scaling,
+                    int32_t dtype, int32_t impl, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+  return add_or_delta(delta, delta_ld, x, x_ld, T, in_dim, n_slices, a_slabs, b_slabs, out_sizes, col_offsets, S, r_max,
+                      rank_per_slot, scale_per_slot, token_to_slot, sorted_idx, slot_ids, counts, offsets, n_buckets,
+                      scaling, dtype, impl, workspace, workspace_bytes, stream, 1);
 }
 
 int lora_b200_shrink(void* out, int32_t out_dtype, const void* x, int64_t x_ld, int32_t T,

@@ -72,8 +72,12 @@ struct BgmvProblem {
   int n_buckets; float scaling;
   // 0 = fused add; 1 = shrink only: tmp_io[s, t, 0:r] = scaling * x[t] . A_s[slot_t]^T (fp32, rows with an
   // adapter only); 2 = expand only: y += tmp_io . B^T. The pair serves the tensor-parallel exchange of tmp.
+  // 3 = overwrite: y[t, cols] = delta for rows with an adapter and -0.0 for every other row (y is not
+  // read); a base GEMM that then accumulates into y (beta = 1) gives base + delta, and x + (-0.0) == x
+  // keeps rows without adapter bit-identical to the base result.
   int mode = 0;
   float* tmp_io = nullptr;  // [n_slices, T, r_max] fp32
+  const int32_t* token_to_slot = nullptr;  // mode 3: which rows have no adapter
 };
 
 struct BgmvParams {
@@ -94,12 +98,32 @@ struct BgmvParams {
   int tmp_bytes;    // bytes of one tmp buffer
   int off_red, off_tmp, off_bar;
   int use_pdl;
-  int mode;         // 0 fused, 1 shrink only (tmp_io written), 2 expand only (tmp_io read)
+  int mode;         // 0 fused, 1 shrink only (tmp_io written), 2 expand only (tmp_io read), 3 overwrite y
   float* tmp_io;
+  const int32_t* token_to_slot;
 };
 
 __host__ __device__ __forceinline__ int ceil_div_i(int a, int b) { return (a + b - 1) / b; }
 __host__ __device__ __forceinline__ int round_up_i(int a, int b) { return ceil_div_i(a, b) * b; }
+
+// mode 3: rows that get no delta (no adapter, unknown slot, adapter of rank 0) are set to -0.0 over the
+// columns of all slices; the rows are dealt over the CTAs of the grid, `nthreads` threads of each taking part.
+__device__ __forceinline__ void bgmv_fill_rows_without_delta(const BgmvParams& p, int cta, int n_ctas, int thread, int nthreads) {
+  const uint4 negz = make_uint4(0x80008000u, 0x80008000u, 0x80008000u, 0x80008000u);
+  for (int row = cta; row < p.T; row += n_ctas) {
+    const int sl = p.token_to_slot[row];
+    bool dead = sl < 0 || sl >= p.S;
+    if (!dead && p.rank_per_slot != nullptr) dead = p.rank_per_slot[sl] <= 0;
+    if (!dead) continue;
+#pragma unroll
+    for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) {
+      if (s < p.st.n) {
+        __nv_bfloat16* dst = p.y + (int64_t)row * p.y_ld + p.st.col[s];
+        for (int i = thread; i < (p.st.out[s] >> 3); i += nthreads) stg128(dst + 8 * i, negz);
+      }
+    }
+  }
+}
 
 #ifndef BGMV_MINBLOCKS
 #define BGMV_MINBLOCKS 1
@@ -146,11 +170,16 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
     mbar_fence_init();
   }
 
-  if (slot < 0 || slot >= p.S || cnt <= 0 || start < 0 || start > p.T - cnt) return;
   int rank = p.r_max;
-  if (p.rank_per_slot != nullptr) rank = min(max(p.rank_per_slot[slot], 0), p.r_max);
+  if (p.rank_per_slot != nullptr && slot >= 0 && slot < p.S) rank = min(max(p.rank_per_slot[slot], 0), p.r_max);
   const int r_eff = min(p.r_max, (rank + 31) & ~31);
-  if (r_eff == 0) return;
+  if (slot < 0 || slot >= p.S || cnt <= 0 || start < 0 || start > p.T - cnt || r_eff == 0) {
+    if (p.mode == 3) {  // an idle cluster still does its share of the -0.0 rows
+      if (p.use_pdl) griddep_wait();
+      bgmv_fill_rows_without_delta(p, bucket * C + c, (int)gridDim.y * C, tid, kBgmvThreads);
+    }
+    return;
+  }
   const float sc = p.scaling * (p.scale_per_slot != nullptr ? p.scale_per_slot[slot] : 1.0f);
   B200_TRACE_POINT(1)
 
@@ -285,7 +314,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
     }
 #pragma unroll
     for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) {
-      if (s < n) {
+      if (s < n && mode != 3) {
         for (int r = warp * 32 + t * 8; r < e_n[s]; r += kBgmvWarps * 32) {
           const int cc = p.st.col[s] + e_lo[s] + r;
           if (tok0_lo >= 0) prefetch_l2(p.y + (int64_t)tok0_lo * p.y_ld + cc);
@@ -295,6 +324,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
     }
     griddep_wait();  // x and y of this launch are final from here on
   }
+  if (mode == 3) bgmv_fill_rows_without_delta(p, bucket * C + c, (int)gridDim.y * C, tid, kBgmvConsumers);
   B200_TRACE_POINT(4)
 
   int c_stage = 0, c_round = 0;  // stage / round of the tile being consumed
@@ -336,7 +366,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
       col_ = cb + lo + r0;
       s_ = ys;
       ++yet;
-      if (warp * 32 + 8 * t < nrows_) {
+      if (mode != 3 && warp * 32 + 8 * t < nrows_) {  // (overwrite: y is not read, the delta is added to zeros)
         const int cc = col_ + warp * 32 + 8 * t;
         if (tok_lo >= 0) lo4 = ldg128(p.y + (int64_t)tok_lo * p.y_ld + cc);
         if (tok_hi >= 0) hi4 = ldg128(p.y + (int64_t)tok_hi * p.y_ld + cc);
@@ -630,7 +660,9 @@ inline bool bgmv_plan(const BgmvProblem& b, BgmvParams* pp, const char** why) {
   p.use_pdl = bgmv_options().pdl ? 1 : 0;
   p.mode = b.mode;
   p.tmp_io = b.tmp_io;
-  if (b.mode != 0 && b.tmp_io == nullptr) { *why = "shrink-only / expand-only need the tmp array"; return false; }
+  p.token_to_slot = b.token_to_slot;
+  if ((b.mode == 1 || b.mode == 2) && b.tmp_io == nullptr) { *why = "shrink-only / expand-only need the tmp array"; return false; }
+  if (b.mode == 3 && b.token_to_slot == nullptr) { *why = "overwrite mode needs token_to_slot"; return false; }
   if (pp != nullptr) *pp = p;
   return true;
 }

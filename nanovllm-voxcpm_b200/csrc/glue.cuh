@@ -33,6 +33,9 @@ __global__ void __launch_bounds__(kGlueThreads) add_rmsnorm_kernel(T* __restrict
                                                                    int64_t x_ld, const T* residual, int64_t res_ld,
                                                                    const T* __restrict__ weight, int T_rows, int H,
                                                                    float eps, int norm_of_rounded_sum) {
+  // a multi-LoRA launch that follows in the stream may start its weight fetch now (it waits for this
+  // kernel's completion before it touches activations)
+  griddep_launch_dependents();
   const int row = blockIdx.x * (kGlueThreads / 32) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= T_rows) return;
@@ -144,6 +147,7 @@ constexpr int kRopeThreads = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(kRopeThreads) rope_kv_store_kernel(const RopeKvParams p) {
+  griddep_launch_dependents();
   const int half = p.D >> 1, vec_per_half = half >> 3;
   const int q_size = p.Hq * p.D, kv_size = p.Hk * p.D, kv_vecs = kv_size >> 3;
   const int rot_items = p.apply_rope ? (p.Hq + p.Hk) * vec_per_half : 0;
@@ -226,6 +230,7 @@ inline int rope_kv_store_launch(const RopeKvParams& p, int dtype, cudaStream_t s
 template <typename T>
 __global__ void __launch_bounds__(kGlueThreads) silu_mul_kernel(T* __restrict__ out, int64_t out_ld,
                                                                 const T* __restrict__ x, int64_t x_ld, int T_rows, int I) {
+  griddep_launch_dependents();
   const int nvec = I >> 3;
   const int64_t total = (int64_t)T_rows * nvec;
   for (int64_t i = (int64_t)blockIdx.x * kGlueThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kGlueThreads) {

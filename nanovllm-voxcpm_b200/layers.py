@@ -34,6 +34,10 @@ from .lora import B200LoRABackend, LoRAMetadata, get_backend
 
 #: opt-in: route large bf16 batches through the fused base-GEMM + LoRA tensor-core kernel
 FUSED_LINEAR = False
+#: True: decode-sized bf16 batches of a layer without bias compute the LoRA delta FIRST (``lora_b200_delta`` into the
+#: output buffer, -0.0 in rows without adapter) and let the base GEMM accumulate into it (``addmm_``), so that the
+#: multi-LoRA launch does not have to wait for the GEMM and can overlap the kernel before it
+LORA_FIRST = False
 
 
 def _get_world_size() -> int:
@@ -147,6 +151,27 @@ class _LoRALayerBase(nn.Module):
                         x_flat, weight, bias, [a[i] for i in active], [b[i] for i in active],
                         [widths[i] for i in active], [cols[i] for i in active], token_to_slot, 1.0,
                     )
+                    return y if x.dim() == 2 else y.view(*x.shape[:-1], y.size(-1))
+        if LORA_FIRST and bias is None and x.is_cuda and isinstance(get_backend(), B200LoRABackend):
+            from .lora import SGMV_MIN_TOKENS, launch_add
+
+            x_flat = x if x.dim() == 2 else x.reshape(-1, x.size(-1))
+            if x_flat.size(0) < SGMV_MIN_TOKENS and x_flat.dtype == torch.bfloat16:
+                token_to_slot = self._resolve_token_slots(x_flat)
+                metadata = self._runtime_metadata()
+                widths, cols = self._slice_layout()
+                active = [i for i, w in enumerate(widths) if w > 0]
+                covered = sorted((cols[i], cols[i] + widths[i]) for i in active)
+                whole = bool(covered) and covered[0][0] == 0 and covered[-1][1] == weight.size(0) and all(
+                    covered[i][1] == covered[i + 1][0] for i in range(len(covered) - 1))
+                if token_to_slot is not None and metadata is not None and whole:
+                    # the delta first (its launch does not wait for the GEMM), then the GEMM accumulates into it
+                    a, b = self._a_slices(), self._b_slices()
+                    y = torch.empty(x_flat.size(0), weight.size(0), dtype=x.dtype, device=x.device)
+                    launch_add(y, x_flat, [a[i] for i in active], [b[i] for i in active], [widths[i] for i in active],
+                               [cols[i] for i in active], metadata, 1.0, rank_per_slot=self.effective_lora_rank,
+                               impl=get_backend().impl, overwrite=True)
+                    y.addmm_(x_flat, weight.t())
                     return y if x.dim() == 2 else y.view(*x.shape[:-1], y.size(-1))
         return self._apply_lora(F.linear(x, weight, bias), x)
 

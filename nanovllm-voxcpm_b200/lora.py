@@ -131,8 +131,10 @@ def launch_add(
     scale_per_slot: torch.Tensor | None = None,
     impl: int = N.IMPL_AUTO,
     workspace: torch.Tensor | None = None,
+    overwrite: bool = False,
 ) -> None:
-    """One ``lora_b200_add`` call: all slices share (slots, rank, in)."""
+    """One ``lora_b200_add`` call: all slices share (slots, rank, in). ``overwrite=True`` is ``lora_b200_delta``:
+    ``y_packed`` receives the delta (and -0.0 in rows without one) instead of being added to."""
     T = x.size(0)
     N.require_cuda(y_packed, x, *a_slabs, *b_slabs, metadata.token_to_slot)
     if y_packed.dim() != 2 or x.dim() != 2:
@@ -169,7 +171,7 @@ def launch_add(
     ):
         workspace = scratch_for(x.device, N.workspace_bytes(T, len(a_slabs), r_max))
     with torch.cuda.device(x.device):
-        rc = N.lib().lora_b200_add(
+        rc = (N.lib().lora_b200_delta if overwrite else N.lib().lora_b200_add)(
             y_packed.data_ptr(), y_packed.stride(0), x.data_ptr(), x.stride(0), T, in_dim, len(a_slabs),
             N.ptr_array(a_slabs), N.ptr_array(b_slabs), N.int_array(out_sizes), N.int_array(col_offsets),
             S, r_max, N.ptr(rank_per_slot), N.ptr(scale_per_slot), tts.data_ptr(), N.ptr(srt), N.ptr(ids),
@@ -439,3 +441,31 @@ def install_into_reference(backend: LoRABackend | None = None) -> LoRABackend:
     backend = backend or B200LoRABackend()
     ref_lora.set_backend_for_testing(backend)
     return backend
+
+
+def prefetch_slabs(slabs, metadata: "LoRAMetadata") -> None:
+    """L2 prefetch hint (``lora_b200_prefetch_slabs``) for the slot regions of ``slabs`` (each ``[S, ...]``
+    contiguous, at most 16 per call) that the step's active buckets will read; launched on the current stream,
+    meant for a side stream one layer ahead of the launches that use the slabs. Needs the bucket arrays
+    (``active_slot_ids`` / ``num_tokens_per_slot``); without them nothing is launched."""
+    if not slabs:
+        return
+    ids, cnt = _i32(metadata.active_slot_ids, "slot ids"), _i32(metadata.num_tokens_per_slot, "counts")
+    if ids is None or cnt is None:
+        return
+    n_buckets = min(ids.numel(), cnt.numel())
+    if metadata.num_active_loras > 0:
+        n_buckets = min(n_buckets, metadata.num_active_loras)
+    if n_buckets <= 0:
+        return
+    N.require_cuda(*slabs, ids, cnt)
+    S = slabs[0].size(0)
+    for t in slabs:
+        if not t.is_contiguous() or t.size(0) != S:
+            raise ValueError("slabs must be contiguous [S, ...] tensors over the same slots")
+    import ctypes
+
+    strides = (ctypes.c_int64 * len(slabs))(*[t.stride(0) * t.element_size() for t in slabs])
+    with torch.cuda.device(ids.device):
+        N.check(N.lib().lora_b200_prefetch_slabs(N.ptr_array(slabs), strides, strides, len(slabs), ids.data_ptr(),
+                                                 cnt.data_ptr(), n_buckets, S, N.current_stream(ids.device)))
