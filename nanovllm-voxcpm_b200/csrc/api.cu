@@ -353,6 +353,15 @@ static int add_or_delta(void* y, int64_t y_ld, const void* x, int64_t x_ld, int3
       return bgmv_launch(bp, st_);
     bp.mode = 0;
     bp.token_to_slot = nullptr;
+    // prefill batches: the tile kernel stores the delta tiles instead of reduce-adding them
+    {
+      int n_act = 0;
+      for (int s = 0; s < st.n; ++s) n_act += st.out[s] > 0;
+      if (dtype == B200_LORA_BF16 && (impl == B200_LORA_IMPL_SGMV || (impl == B200_LORA_IMPL_AUTO && !decode_like)) &&
+          sgmv_supported(sp, nullptr) && prefill_overwrite_ok(st) && workspace != nullptr &&
+          workspace_bytes >= sgmv_workspace_bytes(T, n_act, r_max))
+        return prefill_add_launch(sp, workspace, workspace_bytes, st_, true);
+    }
     fill_neg_zero_kernel<<<(unsigned)T, 128, 0, st_>>>(y, y_ld, st, dtype == B200_LORA_F32 ? 4 : 2);
     if (int rc = check_launch("fill_neg_zero_kernel")) return rc;
   }

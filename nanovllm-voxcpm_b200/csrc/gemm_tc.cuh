@@ -48,6 +48,7 @@ struct GemmArgs {
   const int32_t* token_to_slot;
   int expand_mode;                 // 0 = LINEAR (store), 1 = EXPAND (reduce-add, blocks without -1 rows)
   int lora;                        // LINEAR: add the LoRA stages
+  int overwrite;                   // EXPAND: store the delta tiles (-0.0 in rows without adapter) instead of adding them
 };
 
 struct GemmMaps {
@@ -98,6 +99,22 @@ __device__ __forceinline__ void bulk_wait_group_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 
+// Optional timeline (SM clock) of CTA 0, compiled in only for tuning builds.
+#ifdef B200_TRACE
+#define B200_TILE_TRACE(idx) \
+  if (blockIdx.x == 0 && (idx) < 1024 * 32) g_b200_trace[(idx)] = clock64();
+// wall clock (ns) at entry / exit of every CTA
+#define B200_TILE_TRACE_CTA(which)                                                          \
+  if (threadIdx.x == 0) {                                                                   \
+    unsigned long long t_;                                                                  \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
+    g_b200_trace[2048 + 2 * blockIdx.x + (which)] = (long long)t_;                          \
+  }
+#else
+#define B200_TILE_TRACE(idx)
+#define B200_TILE_TRACE_CTA(which)
+#endif
+
 __global__ void __launch_bounds__(kTileThreads, 1)
 tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -112,6 +129,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int r = a.r_max, n = a.n;
+  B200_TILE_TRACE_CTA(0)
   // Persistent schedule: the output tiles, numbered row block major (id = blk * ntile_all + j), are
   // dealt to the CTAs in equal contiguous ranges, so every SM gets the same number of tiles and a CTA
   // changes row block at most kTileMaxSeg - 1 times.
@@ -168,7 +186,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
     nruns = seg_nruns[sg];
     ja = max(t_begin - blk * ntile_all, 0);
     jb = min(t_end - blk * ntile_all, ntile_all);
-    if (a.expand_mode && nruns == 0) jb = ja;
+    if (a.expand_mode && nruns == 0 && !a.overwrite) jb = ja;
   };
   const int row_bytes = r * 2;
   const uint32_t t_tile_bytes = (uint32_t)kSgmvBM * r * 2, b_tile_bytes = (uint32_t)kSgmvBN * r * 2;
@@ -202,6 +220,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
             mbar_arrive_expect_tx(full_bar(st), t_tile_bytes + b_tile_bytes);
             tma_load_2d(base, &maps.t, 0, s * a.T + blk * kSgmvBM, full_bar(st));
             tma_load_2d(base + t_tile_bytes, &maps.b[s], 0, slot * a.out[s] + (lo - a.col[s]), full_bar(st));
+            B200_TILE_TRACE(768 + min(j - ja, 63) + 64 * sg)
             if (++st == kGemmStages) { st = 0; ++round; }
           }
         }
@@ -231,13 +250,16 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
           if (lo >= hi) continue;
           mbar_wait_bounded(full_bar(st), (uint32_t)(round & 1), &abort_flag);
           if (lo_row > 0 || hi_row < kSgmvBM) {
+            // only the rows outside the run are visited: `chunks` lanes per row (its 16-byte pieces; the swizzle
+            // only permutes them inside the row), 32 / chunks rows per step
             const uint32_t base = smem_base + (uint32_t)st * kGemmStageBytes;
-            const int chunks = row_bytes >> 4;  // 16-byte pieces of a row (the swizzle only permutes them inside the row)
-            for (int i = lane; i < kSgmvBM * chunks; i += 32) {
-              const int row = i / chunks;
-              if (row < lo_row || row >= hi_row)
-                asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(base + (uint32_t)i * 16u), "r"(0u) : "memory");
-            }
+            const int chunks = row_bytes >> 4;
+            const int rows_per_step = 32 / chunks, sub = lane / chunks;
+            const uint32_t piece = (uint32_t)(lane - sub * chunks) * 16u;
+            for (int row = sub; row < lo_row; row += rows_per_step)
+              asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(base + (uint32_t)(row * row_bytes) + piece), "r"(0u) : "memory");
+            for (int row = hi_row + sub; row < kSgmvBM; row += rows_per_step)
+              asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(base + (uint32_t)(row * row_bytes) + piece), "r"(0u) : "memory");
             fence_proxy_async_smem();
           }
           __syncwarp();
@@ -259,6 +281,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
         const int buf = job & 1;
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kSgmvBN);
         if (job >= 2) mbar_wait_bounded(acc_empty(buf), (uint32_t)(((job >> 1) - 1) & 1), &abort_flag);
+        B200_TILE_TRACE(512 + 4 * min(job, 31) + 0)
         tc_fence_after_sync();
         for (int kc = 0; kc < nk; ++kc) {
           mbar_wait_bounded(full_bar(st), (uint32_t)(round & 1), &abort_flag);
@@ -278,6 +301,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
             const int lo = max(a.col[s], j * kSgmvBN), hi = min(a.col[s] + a.out[s], (j + 1) * kSgmvBN);
             if (lo >= hi) continue;
             mbar_wait_bounded(masked_bar(st), (mphase >> st) & 1u, &abort_flag);
+            B200_TILE_TRACE(512 + 4 * min(job, 31) + 1)
             mphase ^= 1u << st;
             tc_fence_after_sync();
             const uint32_t base = smem_base + (uint32_t)st * kGemmStageBytes;
@@ -294,6 +318,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
           }
         }
         umma_commit(acc_full(buf));
+        B200_TILE_TRACE(512 + 4 * min(job, 31) + 2)
       }
       }
     }
@@ -311,6 +336,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
     for (int j = ja; j < jb; ++j, ++job) {
       const int buf = job & 1;
       mbar_wait_bounded(acc_full(buf), (uint32_t)((job >> 1) & 1), &abort_flag);
+      if (etid == 0) { B200_TILE_TRACE(16 * min(job, 31) + 0) }
       tc_fence_after_sync();
       for (int c = 0; c < kSgmvBN; c += kGemmOutChunk, ++chunk_no) {
         const int col0 = j * kSgmvBN + c;
@@ -318,6 +344,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
         const uint32_t obuf = out_base + (uint32_t)(chunk_no % kGemmOutBufs) * kGemmOutBufBytes;
         // the store that last used this buffer must have finished reading it
         if (etid == 0) bulk_wait_group_read<kGemmOutBufs - 1>();
+        if (etid == 0) { B200_TILE_TRACE(16 * min(job, 31) + 1 + 3 * (c / kGemmOutChunk)) }
         named_bar_sync(2, 128);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -347,21 +374,25 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
                          : "memory");
           }
         }
+        if (etid == 0) { B200_TILE_TRACE(16 * min(job, 31) + 2 + 3 * (c / kGemmOutChunk)) }
         fence_proxy_async_smem();
         named_bar_sync(2, 128);
+        if (etid == 0) { B200_TILE_TRACE(16 * min(job, 31) + 3 + 3 * (c / kGemmOutChunk)) }
         if (etid == 0) {
-          if (a.expand_mode) tma_reduce_add_2d(&maps.y, obuf, col0, blk * kSgmvBM);
+          if (a.expand_mode && !a.overwrite) tma_reduce_add_2d(&maps.y, obuf, col0, blk * kSgmvBM);
           else tma_store_2d_hint(&maps.y, obuf, col0, blk * kSgmvBM, l2_policy_evict_first());
           bulk_commit_group();
         }
       }
       tc_fence_before_sync();
       mbar_arrive(acc_empty(buf));
+      if (etid == 0) { B200_TILE_TRACE(16 * min(job, 31) + 13) }
     }
     }
     if (etid == 0) bulk_wait_group_read<0>();
   }
   __syncthreads();
+  B200_TILE_TRACE_CTA(1)
   if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)tmem_cols);
   if (tid == 0 && abort_flag != 0) atomicOr(&g_b200_status, kStatusWaitGaveUp);
 }
@@ -389,7 +420,8 @@ inline bool tc_lora_stage_ok(const SgmvArgs& a) {
 // Tensor maps / arguments of tc_tile_kernel from the prefill kernels' (sgmv_prepare) ones.
 // `weight` [n_total, in] row-major with pitch w_ld (LINEAR) or null (EXPAND).
 inline int tc_tile_prepare(const SgmvMaps& sm, const SgmvArgs& sa, const void* weight, int64_t w_ld, int n_total,
-                           const void* bias, bool expand_mode, bool lora, GemmMaps* maps, GemmArgs* args) {
+                           const void* bias, bool expand_mode, bool lora, GemmMaps* maps, GemmArgs* args,
+                           bool overwrite = false) {
   GemmArgs a = {};
   a.T = sa.T; a.in_dim = expand_mode ? 0 : sa.in_dim; a.n_total = n_total;
   a.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -398,6 +430,7 @@ inline int tc_tile_prepare(const SgmvMaps& sm, const SgmvArgs& sa, const void* w
   a.token_to_slot = sa.token_to_slot;
   a.expand_mode = expand_mode ? 1 : 0;
   a.lora = lora ? 1 : 0;
+  a.overwrite = overwrite ? 1 : 0;
   maps->x = sm.x; maps->t = sm.t;
   for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) maps->b[s] = sm.b[s];
   maps->w = sm.x;
@@ -427,17 +460,31 @@ inline int tc_tile_launch(const GemmMaps& maps, const GemmArgs& a, cudaStream_t 
 
 // y += LoRA delta for a prefill batch: shrink, then the reduce-add tile kernel (or the run-based
 // expand when the slices do not tile the output in 64-column units).
-inline int prefill_add_launch(const SgmvProblem& b, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+// overwrite: y = delta (rows without adapter: -0.0) through plain tile stores, no read of y; only when the
+// slices tile the output (prefill_overwrite_ok).
+inline bool prefill_overwrite_ok(const SliceTable& st) {
+  int pos = 0;
+  for (int s = 0; s < st.n; ++s) {
+    if (st.out[s] == 0) continue;
+    if (st.col[s] != pos || st.out[s] % kGemmOutChunk != 0) return false;
+    pos += st.out[s];
+  }
+  return pos > 0;
+}
+
+inline int prefill_add_launch(const SgmvProblem& b, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                              bool overwrite = false) {
   SgmvMaps sm;
   SgmvArgs sa;
   if (int rc = sgmv_prepare(b, workspace, workspace_bytes, &sm, &sa)) return rc;
+  if (overwrite && !tc_expand_fast_path_ok(sa)) return fail(B200_LORA_EUNSUPPORTED, "prefill overwrite: slices do not tile the output");
   if (int rc = sgmv_launch_shrink(sm, sa, stream)) return rc;
   int n_total = 0;
   for (int s = 0; s < sa.n; ++s) n_total = std::max(n_total, sa.col[s] + sa.out[s]);
   if (tc_expand_fast_path_ok(sa)) {
     GemmMaps gm;
     GemmArgs ga;
-    if (int rc = tc_tile_prepare(sm, sa, nullptr, 0, n_total, nullptr, true, true, &gm, &ga)) return rc;
+    if (int rc = tc_tile_prepare(sm, sa, nullptr, 0, n_total, nullptr, true, true, &gm, &ga, overwrite)) return rc;
     return tc_tile_launch(gm, ga, stream);
   }
   return sgmv_launch_expand(sm, sa, stream);

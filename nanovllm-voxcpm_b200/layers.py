@@ -34,9 +34,10 @@ from .lora import B200LoRABackend, LoRAMetadata, get_backend
 
 #: opt-in: route large bf16 batches through the fused base-GEMM + LoRA tensor-core kernel
 FUSED_LINEAR = False
-#: True: decode-sized bf16 batches of a layer without bias compute the LoRA delta FIRST (``lora_b200_delta`` into the
-#: output buffer, -0.0 in rows without adapter) and let the base GEMM accumulate into it (``addmm_``), so that the
-#: multi-LoRA launch does not have to wait for the GEMM and can overlap the kernel before it
+#: True: bf16 batches of a layer without bias compute the LoRA delta FIRST (``lora_b200_delta`` into the output
+#: buffer, -0.0 in rows without adapter) and let the base GEMM accumulate into it (``addmm_``): in decode the
+#: multi-LoRA launch no longer waits for the GEMM and overlaps the kernel before it, in prefill the delta tiles are
+#: stored instead of being reduce-added into y
 LORA_FIRST = False
 
 
@@ -153,10 +154,10 @@ class _LoRALayerBase(nn.Module):
                     )
                     return y if x.dim() == 2 else y.view(*x.shape[:-1], y.size(-1))
         if LORA_FIRST and bias is None and x.is_cuda and isinstance(get_backend(), B200LoRABackend):
-            from .lora import SGMV_MIN_TOKENS, launch_add
+            from .lora import launch_add
 
             x_flat = x if x.dim() == 2 else x.reshape(-1, x.size(-1))
-            if x_flat.size(0) < SGMV_MIN_TOKENS and x_flat.dtype == torch.bfloat16:
+            if x_flat.dtype == torch.bfloat16:
                 token_to_slot = self._resolve_token_slots(x_flat)
                 metadata = self._runtime_metadata()
                 widths, cols = self._slice_layout()

@@ -95,8 +95,27 @@ def test_delta_on_the_other_paths():
     want = O.add_lora(torch.zeros_like(p.y), p.x, p.a_slabs, p.b_slabs, p.token_to_slot, 1.0, p.col_offsets)
     assert_lora_close(y.cpu(), want, what="fp16 generic")
     assert bool((y.cpu()[p.token_to_slot < 0].view(torch.int16) == NEG_ZERO).all())
-    p = W.prefill_projection("o", seed=2)
-    check_delta(p, run_delta(p, N.IMPL_AUTO, "eager"), "prefill")
+    # slices that do not tile the output in 64-column units: fill, then the prefill kernels add
+    p = W.make_projection(5, 600, 256, [96, 160], 4, 32, p_none=0.0,
+                          token_to_slot=[i // 150 for i in range(600)])
+    check_delta(p, run_delta(p, N.IMPL_AUTO, "eager"), "prefill, odd slices")
+
+
+@pytest.mark.parametrize("name", ["qkv", "o", "gate_up", "down"])
+def test_prefill_delta_is_stored_by_the_tile_kernel(name):
+    p = W.prefill_projection(name, seed=2)
+    check_delta(p, run_delta(p, N.IMPL_AUTO, "eager", pad=64), f"prefill {name}")
+
+
+def test_prefill_delta_mixed_blocks_and_rows_without_adapter():
+    """Runs of different slots inside one 128-row block, rows and whole blocks without adapter, ragged last block."""
+    gen = torch.Generator().manual_seed(9)
+    T, S = 1000, 6
+    slots = torch.repeat_interleave(torch.randint(-1, S, (40,), generator=gen), 25)
+    slots[256:512] = -1   # two whole row blocks without adapter
+    p = W.make_projection(7, T, 512, [256, 128, 128], S, 64, ranks=[8, 16, 64, 64, 32, 16], token_to_slot=slots.tolist())
+    check_delta(p, run_delta(p, N.IMPL_AUTO, "eager"), "mixed blocks")
+    check_delta(p, run_delta(p, N.IMPL_SGMV, "eager"), "mixed blocks / SGMV")
 
 
 @pytest.mark.parametrize("kind", ["qkv", "gate_up", "row"])
