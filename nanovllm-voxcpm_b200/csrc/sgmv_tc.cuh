@@ -34,7 +34,8 @@ struct SgmvArgs {
   const float* scale_per_slot; float scaling;
   int zero_fill;                            // shrink: write zero rows for tokens without adapter
   int skip_clean;                           // expand: leave blocks in which every row has an adapter to tc_tile_kernel
-  int shrink_stages;                        // shrink: depth of the TMA ring (set by the launch)
+  int shrink_gmax;                          // shrink: runs of a block whose K loops share one pass over x (set by the launch)
+  int shrink_ring_bytes;                    // shrink: bytes of the TMA ring (set by the launch)
 };
 
 struct SgmvMaps {
@@ -88,6 +89,22 @@ __device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const uint32_t
   }
 }
 
+// Optional timeline of tuning builds: wall clock (ns) at entry / exit of every shrink CTA, SM clock at the
+// k-steps of CTA 0's MMA thread.
+#ifdef B200_TRACE
+#define B200_SHRINK_TRACE_CTA(which)                                                        \
+  if (threadIdx.x == 0 && blockIdx.x < 512) {                                               \
+    unsigned long long t_;                                                                  \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
+    g_b200_trace[4096 + 2 * blockIdx.x + (which)] = (long long)t_;                          \
+  }
+#define B200_SHRINK_TRACE_K(i) \
+  if (blockIdx.x == 0 && (i) < 256) g_b200_trace[6144 + (i)] = clock64();
+#else
+#define B200_SHRINK_TRACE_CTA(which)
+#define B200_SHRINK_TRACE_K(i)
+#endif
+
 // ============================================================================ shrink
 __global__ void __launch_bounds__(kSgmvThreads, 1)
 sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
@@ -100,10 +117,10 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int blk = blockIdx.x;
-  const int r = a.r_max, n = a.n, NS = a.shrink_stages;
+  const int r = a.r_max, n = a.n;
+  B200_SHRINK_TRACE_CTA(0)
   const uint32_t a_tile_bytes = (uint32_t)r * kSgmvBK * 2;
   const uint32_t x_tile_bytes = kSgmvBM * kSgmvBK * 2;
-  const uint32_t stage_bytes = x_tile_bytes + (uint32_t)n * a_tile_bytes;
   const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * (uint32_t)s; };
@@ -111,10 +128,10 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
   const uint32_t acc_full = bar0 + 8u * (2 * kSgmvShrinkMaxStages);
   const uint32_t acc_empty = acc_full + 8u;
   int tmem_cols = 32;  // the last slice is read in 32-column chunks
-  while (tmem_cols < (n - 1) * r + ((r + 31) & ~31)) tmem_cols *= 2;
+  while (tmem_cols < (a.shrink_gmax * n - 1) * r + ((r + 31) & ~31)) tmem_cols *= 2;
 
   if (tid == 0) {
-    for (int s = 0; s < NS; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < kSgmvShrinkMaxStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 128);
     abort_flag = 0;
@@ -129,21 +146,32 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
   const uint32_t tmem_base = tmem_base_s;
   const int nruns = nruns_s;
   const int nk = a.in_dim / kSgmvBK;
+  // The runs of a block (two at a request boundary) share ONE pass over x: every K step loads the x tile once
+  // and one lora_A tile per run and slice, and the MMAs of run i accumulate into their own TMEM columns
+  // [(i * n + s) * r, +r). Up to G runs per pass; the ring depth follows from the stage size of this block.
+  const int G = min(a.shrink_gmax, max(nruns, 1));
+  const uint32_t stage_bytes = x_tile_bytes + (uint32_t)(G * n) * a_tile_bytes;
+  const int NS = min(kSgmvShrinkMaxStages, (int)((uint32_t)a.shrink_ring_bytes / stage_bytes));
+  const int npass = (nruns + G - 1) / G;
 
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&maps.x);
       for (int s = 0; s < n; ++s) tma_prefetch_desc(&maps.a[s]);
       int st = 0, round = 0;
-      for (int u = 0; u < nruns; ++u) {
-        const int slot = run_slot[u];
+      for (int pi = 0; pi < npass; ++pi) {
+        const int u0 = pi * G, g = min(G, nruns - u0);
         for (int kc = 0; kc < nk; ++kc) {
           if (round > 0) mbar_wait_bounded(empty_bar(st), (uint32_t)((round & 1) ^ 1), &abort_flag);
           const uint32_t base = smem_base + (uint32_t)st * stage_bytes;
-          mbar_arrive_expect_tx(full_bar(st), stage_bytes);
+          mbar_arrive_expect_tx(full_bar(st), x_tile_bytes + (uint32_t)(g * n) * a_tile_bytes);
           tma_load_2d(base, &maps.x, kc * kSgmvBK, blk * kSgmvBM, full_bar(st));
-          for (int s = 0; s < n; ++s)
-            tma_load_2d(base + x_tile_bytes + (uint32_t)s * a_tile_bytes, &maps.a[s], kc * kSgmvBK, slot * r, full_bar(st));
+          for (int ui = 0; ui < g; ++ui) {
+            const int slot = run_slot[u0 + ui];
+            for (int s = 0; s < n; ++s)
+              tma_load_2d(base + x_tile_bytes + (uint32_t)(ui * n + s) * a_tile_bytes, &maps.a[s], kc * kSgmvBK, slot * r,
+                          full_bar(st));
+          }
           if (++st == NS) { st = 0; ++round; }
         }
       }
@@ -152,19 +180,21 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(kSgmvBM, r);
       int st = 0, round = 0;
-      for (int u = 0; u < nruns; ++u) {
-        if (u > 0) mbar_wait_bounded(acc_empty, (uint32_t)((u - 1) & 1), &abort_flag);
+      for (int pi = 0; pi < npass; ++pi) {
+        const int g = min(G, nruns - pi * G);
+        if (pi > 0) mbar_wait_bounded(acc_empty, (uint32_t)((pi - 1) & 1), &abort_flag);
         tc_fence_after_sync();
         for (int kc = 0; kc < nk; ++kc) {
           mbar_wait_bounded(full_bar(st), (uint32_t)(round & 1), &abort_flag);
+          B200_SHRINK_TRACE_K(kc)
           tc_fence_after_sync();
           const uint32_t base = smem_base + (uint32_t)st * stage_bytes;
           const uint64_t xdesc = umma_smem_desc(base, 128);
-          for (int s = 0; s < n; ++s) {
-            const uint64_t adesc = umma_smem_desc(base + x_tile_bytes + (uint32_t)s * a_tile_bytes, 128);
+          for (int q = 0; q < g * n; ++q) {  // q = run in pass * n + slice
+            const uint64_t adesc = umma_smem_desc(base + x_tile_bytes + (uint32_t)q * a_tile_bytes, 128);
 #pragma unroll
             for (int k4 = 0; k4 < kSgmvBK / 16; ++k4)
-              umma_bf16(tmem_base + (uint32_t)(s * r), xdesc + 2u * k4, adesc + 2u * k4, idesc, (kc > 0 || k4 > 0) ? 1u : 0u);
+              umma_bf16(tmem_base + (uint32_t)(q * r), xdesc + 2u * k4, adesc + 2u * k4, idesc, (kc > 0 || k4 > 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(st));  // stage reusable once these MMAs have read it
           if (++st == NS) { st = 0; ++round; }
@@ -183,18 +213,26 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
         for (int c = 0; c < r; c += 8) stg128(dst + c, make_uint4(0, 0, 0, 0));
       }
     }
-    for (int u = 0; u < nruns; ++u) {
-      mbar_wait_bounded(acc_full, (uint32_t)(u & 1), &abort_flag);
+    for (int pi = 0; pi < npass; ++pi) {
+      const int u0 = pi * G, g = min(G, nruns - u0);
+      mbar_wait_bounded(acc_full, (uint32_t)(pi & 1), &abort_flag);
       tc_fence_after_sync();
-      const bool mine = row_in_blk >= run_lo[u] && row_in_blk < run_hi[u] && row < a.T;
-      const int slot = run_slot[u];
-      const float sc = a.scaling * (a.scale_per_slot != nullptr ? a.scale_per_slot[slot] : 1.0f);
-      for (int s = 0; s < n; ++s) {
-        for (int c = 0; c < r; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(s * r + c), v);
-          tmem_ld_wait();
-          if (mine) store_bf16x32(a.tmp + ((int64_t)s * a.T + row) * r + c, v, sc, min(32, r - c));
+      for (int ui = 0; ui < g; ++ui) {
+        const int u = u0 + ui;
+        // (a TMEM load is a warp-wide operation on one column range: a warp whose 32 rows straddle two runs
+        //  reads both runs' columns and every lane keeps the ones of its own run)
+        const int lo_row = run_lo[u], hi_row = run_hi[u];
+        if (hi_row <= quarter * 32 || lo_row >= quarter * 32 + 32) continue;  // warp-uniform: no row of this warp
+        const bool mine = row_in_blk >= lo_row && row_in_blk < hi_row && row < a.T;
+        const int slot = run_slot[u];
+        const float sc = a.scaling * (a.scale_per_slot != nullptr ? a.scale_per_slot[slot] : 1.0f);
+        for (int s = 0; s < n; ++s) {
+          for (int c = 0; c < r; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((ui * n + s) * r + c), v);
+            tmem_ld_wait();
+            if (mine) store_bf16x32(a.tmp + ((int64_t)s * a.T + row) * r + c, v, sc, min(32, r - c));
+          }
         }
       }
       tc_fence_before_sync();
@@ -202,6 +240,7 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
     }
   }
   __syncthreads();
+  B200_SHRINK_TRACE_CTA(1)
   if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)tmem_cols);
   if (tid == 0 && abort_flag != 0) atomicOr(&g_b200_status, kStatusWaitGaveUp);
 }
@@ -417,10 +456,19 @@ inline int sgmv_set_smem(const void* kernel, size_t bytes) {
 
 inline int sgmv_launch_shrink(const SgmvMaps& maps, const SgmvArgs& a_in, cudaStream_t stream) {
   SgmvArgs a = a_in;
-  // one CTA per SM streams its 128 rows of x: the deeper the ring, the more bytes are in flight per SM
-  const size_t stage = kSgmvBM * kSgmvBK * 2 + (size_t)a.n * a.r_max * kSgmvBK * 2;
-  a.shrink_stages = (int)std::min<size_t>(kSgmvShrinkMaxStages, std::max<size_t>(2, (size_t)(216 * 1024) / stage));
-  const size_t smem = (size_t)a.shrink_stages * stage + 1024;
+  // One CTA per SM streams its 128 rows of x through a ring that fills the shared memory of the SM: the more
+  // bytes in flight, the better. Up to 4 runs of a block share a pass, as long as their accumulators fit into
+  // the 512 TMEM columns and three stages of that size fit into the ring.
+  const size_t ring = 216 * 1024;
+  const size_t x_tile = kSgmvBM * kSgmvBK * 2, a_tiles = (size_t)a.n * a.r_max * kSgmvBK * 2;
+  int gmax = 1;
+  for (int g = 2; g <= 4; ++g) {
+    const int cols = (g * a.n - 1) * a.r_max + ((a.r_max + 31) & ~31);
+    if (cols <= 512 && ring / (x_tile + g * a_tiles) >= 3) gmax = g;
+  }
+  a.shrink_gmax = gmax;
+  a.shrink_ring_bytes = (int)ring;
+  const size_t smem = ring + 1024;
   if (int rc = sgmv_set_smem(reinterpret_cast<const void*>(sgmv_shrink_kernel), smem)) return rc;
   const int nblk = (a.T + kSgmvBM - 1) / kSgmvBM;
   sgmv_shrink_kernel<<<nblk, kSgmvThreads, smem, stream>>>(maps, a);
