@@ -19,6 +19,7 @@ namespace b200lora {
 
 constexpr int kSgmvThreads = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
 constexpr int kSgmvBM = 128;        // rows per block / MMA M
+constexpr int kShrinkRows = 64;     // rows of x one shrink CTA owns (the upper half of its M = 128 tiles is idle)
 constexpr int kSgmvBK = 64;         // K columns per shrink stage (one 128-byte swizzle row)
 constexpr int kSgmvBN = 256;        // output columns per expand tile
 constexpr int kSgmvShrinkMaxStages = 8;  // the launch picks as many 64-column stages as fit into shared memory
@@ -40,6 +41,7 @@ struct SgmvArgs {
 
 struct SgmvMaps {
   CUtensorMap x;                            // [T, in]            box 128 x 64
+  CUtensorMap xs;                           // [T, in]            box  64 x 64 (shrink)
   CUtensorMap a[B200_LORA_MAX_SLICES];      // [S*r_max, in]      box r_max x 64
   CUtensorMap t;                            // [n*T, r_max]       box 128 x r_max
   CUtensorMap b[B200_LORA_MAX_SLICES];      // [S*out_s, r_max]   box 256 x r_max
@@ -47,11 +49,11 @@ struct SgmvMaps {
 
 // Runs of equal slot inside block `blk`, written to shared memory by thread 0.
 // (table element types are the caller's: slot ids fit int16 for S <= 32767, row bounds 0..128 fit uint8)
-template <typename TS, typename TR>
+template <typename TS, typename TR, int ROWS = kSgmvBM>
 __device__ __forceinline__ void sgmv_find_runs(const int32_t* tts, int T, int S, int blk, TS* s_slot, TS* run_slot,
                                                TR* run_lo, TR* run_hi, int* nruns) {
-  const int row0 = blk * kSgmvBM;
-  for (int i = threadIdx.x; i < kSgmvBM; i += blockDim.x) {
+  const int row0 = blk * ROWS;
+  for (int i = threadIdx.x; i < ROWS; i += blockDim.x) {
     const int row = row0 + i;
     int sl = -1;
     if (row < T) sl = tts[row];
@@ -61,11 +63,11 @@ __device__ __forceinline__ void sgmv_find_runs(const int32_t* tts, int T, int S,
   __syncthreads();
   if (threadIdx.x == 0) {
     int n = 0, i = 0;
-    while (i < kSgmvBM) {
+    while (i < ROWS) {
       const int sl = s_slot[i];
       if (sl < 0) { ++i; continue; }
       int j = i + 1;
-      while (j < kSgmvBM && s_slot[j] == sl) ++j;
+      while (j < ROWS && s_slot[j] == sl) ++j;
       run_slot[n] = (TS)sl; run_lo[n] = (TR)i; run_hi[n] = (TR)j; ++n;
       i = j;
     }
@@ -119,8 +121,13 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
   const int blk = blockIdx.x;
   const int r = a.r_max, n = a.n;
   B200_SHRINK_TRACE_CTA(0)
+  // A CTA owns kShrinkRows = 64 rows of x: twice as many CTAs as 128-row blocks, so that most SMs of the GPU
+  // stream x (a CTA's rate is bound by the bytes its ring keeps in flight). The MMAs stay M = 128: the x slot of a
+  // stage has room for 128 rows, TMA fills the lower 64, the upper 64 hold stale bytes whose accumulator rows
+  // (TMEM lanes 64..127) are never read.
   const uint32_t a_tile_bytes = (uint32_t)r * kSgmvBK * 2;
   const uint32_t x_tile_bytes = kSgmvBM * kSgmvBK * 2;
+  const uint32_t x_load_bytes = kShrinkRows * kSgmvBK * 2;
   const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * (uint32_t)s; };
@@ -133,7 +140,7 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
   if (tid == 0) {
     for (int s = 0; s < kSgmvShrinkMaxStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 128);
+    mbar_init(acc_empty, kShrinkRows);
     abort_flag = 0;
     mbar_fence_init();
   }
@@ -141,7 +148,7 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
     tmem_alloc(smem_u32(&tmem_base_s), (uint32_t)tmem_cols);
     tc_fence_before_sync();
   }
-  sgmv_find_runs(a.token_to_slot, a.T, a.S, blk, s_slot, run_slot, run_lo, run_hi, &nruns_s);  // has __syncthreads
+  sgmv_find_runs<int, int, kShrinkRows>(a.token_to_slot, a.T, a.S, blk, s_slot, run_slot, run_lo, run_hi, &nruns_s);  // has __syncthreads
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
   const int nruns = nruns_s;
@@ -156,7 +163,7 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
 
   if (warp == 0) {
     if (lane == 0) {
-      tma_prefetch_desc(&maps.x);
+      tma_prefetch_desc(&maps.xs);
       for (int s = 0; s < n; ++s) tma_prefetch_desc(&maps.a[s]);
       int st = 0, round = 0;
       for (int pi = 0; pi < npass; ++pi) {
@@ -164,8 +171,8 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
         for (int kc = 0; kc < nk; ++kc) {
           if (round > 0) mbar_wait_bounded(empty_bar(st), (uint32_t)((round & 1) ^ 1), &abort_flag);
           const uint32_t base = smem_base + (uint32_t)st * stage_bytes;
-          mbar_arrive_expect_tx(full_bar(st), x_tile_bytes + (uint32_t)(g * n) * a_tile_bytes);
-          tma_load_2d(base, &maps.x, kc * kSgmvBK, blk * kSgmvBM, full_bar(st));
+          mbar_arrive_expect_tx(full_bar(st), x_load_bytes + (uint32_t)(g * n) * a_tile_bytes);
+          tma_load_2d(base, &maps.xs, kc * kSgmvBK, blk * kShrinkRows, full_bar(st));
           for (int ui = 0; ui < g; ++ui) {
             const int slot = run_slot[u0 + ui];
             for (int s = 0; s < n; ++s)
@@ -202,11 +209,12 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
         umma_commit(acc_full);
       }
     }
-  } else {
-    // epilogue: thread <-> row; a warp may only touch its own quarter of the 128 TMEM lanes
+  } else if ((warp & 3) < kShrinkRows / 32) {
+    // epilogue: thread <-> row; a warp may only touch its own quarter of the 128 TMEM lanes (the warps of the
+    // idle upper half have nothing to do)
     const int quarter = warp & 3;
     const int row_in_blk = quarter * 32 + lane;
-    const int row = blk * kSgmvBM + row_in_blk;
+    const int row = blk * kShrinkRows + row_in_blk;
     if (a.zero_fill && row < a.T && s_slot[row_in_blk] < 0) {
       for (int s = 0; s < n; ++s) {
         __nv_bfloat16* dst = a.tmp + ((int64_t)s * a.T + row) * r;
@@ -438,6 +446,7 @@ inline int sgmv_prepare(const SgmvProblem& b, void* workspace, size_t workspace_
   a.token_to_slot = b.token_to_slot; a.scale_per_slot = b.scale_per_slot; a.scaling = b.scaling;
   a.zero_fill = 0;
   if (int rc = make_tmap_2d(&maps->x, b.x, (uint64_t)b.T, (uint64_t)b.in_dim, (uint64_t)b.x_ld, kSgmvBM, kSgmvBK)) return rc;
+  if (int rc = make_tmap_2d(&maps->xs, b.x, (uint64_t)b.T, (uint64_t)b.in_dim, (uint64_t)b.x_ld, kShrinkRows, kSgmvBK)) return rc;
   if (int rc = make_tmap_2d(&maps->t, a.tmp, (uint64_t)a.n * b.T + kSgmvBM, (uint64_t)b.r_max, (uint64_t)b.r_max, kSgmvBM, (uint32_t)b.r_max)) return rc;
   for (int s = 0; s < a.n; ++s) {
     if (int rc = make_tmap_2d(&maps->a[s], slab_a[s], (uint64_t)b.S * b.r_max, (uint64_t)b.in_dim, (uint64_t)b.in_dim, (uint32_t)b.r_max, kSgmvBK)) return rc;
@@ -470,7 +479,7 @@ inline int sgmv_launch_shrink(const SgmvMaps& maps, const SgmvArgs& a_in, cudaSt
   a.shrink_ring_bytes = (int)ring;
   const size_t smem = ring + 1024;
   if (int rc = sgmv_set_smem(reinterpret_cast<const void*>(sgmv_shrink_kernel), smem)) return rc;
-  const int nblk = (a.T + kSgmvBM - 1) / kSgmvBM;
+  const int nblk = (a.T + kShrinkRows - 1) / kShrinkRows;
   sgmv_shrink_kernel<<<nblk, kSgmvThreads, smem, stream>>>(maps, a);
   return check_launch("sgmv_shrink_kernel");
 }
