@@ -131,6 +131,8 @@ __device__ __forceinline__ void bgmv_fill_rows_without_delta(const BgmvParams& p
 #ifndef BGMV_YDEPTH
 #define BGMV_YDEPTH 2
 #endif
+// kOverwrite = mode 3, compiled separately so that the add path carries none of its branches
+template <bool kOverwrite>
 __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kernel(const __grid_constant__ BgmvParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -174,7 +176,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
   if (p.rank_per_slot != nullptr && slot >= 0 && slot < p.S) rank = min(max(p.rank_per_slot[slot], 0), p.r_max);
   const int r_eff = min(p.r_max, (rank + 31) & ~31);
   if (slot < 0 || slot >= p.S || cnt <= 0 || start < 0 || start > p.T - cnt || r_eff == 0) {
-    if (p.mode == 3) {  // an idle cluster still does its share of the -0.0 rows
+    if (kOverwrite) {  // an idle cluster still does its share of the -0.0 rows
       if (p.use_pdl) griddep_wait();
       bgmv_fill_rows_without_delta(p, bucket * C + c, (int)gridDim.y * C, tid, kBgmvThreads);
     }
@@ -314,7 +316,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
     }
 #pragma unroll
     for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) {
-      if (s < n && mode != 3) {
+      if (s < n && !kOverwrite) {
         for (int r = warp * 32 + t * 8; r < e_n[s]; r += kBgmvWarps * 32) {
           const int cc = p.st.col[s] + e_lo[s] + r;
           if (tok0_lo >= 0) prefetch_l2(p.y + (int64_t)tok0_lo * p.y_ld + cc);
@@ -324,7 +326,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
     }
     griddep_wait();  // x and y of this launch are final from here on
   }
-  if (mode == 3) bgmv_fill_rows_without_delta(p, bucket * C + c, (int)gridDim.y * C, tid, kBgmvConsumers);
+  if (kOverwrite) bgmv_fill_rows_without_delta(p, bucket * C + c, (int)gridDim.y * C, tid, kBgmvConsumers);
   B200_TRACE_POINT(4)
 
   int c_stage = 0, c_round = 0;  // stage / round of the tile being consumed
@@ -366,7 +368,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
       col_ = cb + lo + r0;
       s_ = ys;
       ++yet;
-      if (mode != 3 && warp * 32 + 8 * t < nrows_) {  // (overwrite: y is not read, the delta is added to zeros)
+      if (!kOverwrite && warp * 32 + 8 * t < nrows_) {  // (overwrite: y is not read, the delta is added to zeros)
         const int cc = col_ + warp * 32 + 8 * t;
         if (tok_lo >= 0) lo4 = ldg128(p.y + (int64_t)tok_lo * p.y_ld + cc);
         if (tok_hi >= 0) hi4 = ldg128(p.y + (int64_t)tok_hi * p.y_ld + cc);
@@ -678,7 +680,9 @@ inline int bgmv_launch(const BgmvProblem& b, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_device != dev) {
-    cudaError_t e = cudaFuncSetAttribute(bgmv_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBgmvSmemMax);
+    cudaError_t e = cudaFuncSetAttribute(bgmv_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBgmvSmemMax);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(bgmv_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBgmvSmemMax);
     if (e != cudaSuccess) return fail(B200_LORA_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured_device = dev;
   }
@@ -701,7 +705,8 @@ inline int bgmv_launch(const BgmvProblem& b, cudaStream_t stream) {
   }
   cfg.attrs = attrs;
   cfg.numAttrs = (unsigned)na;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, bgmv_fused_kernel, p);
+  cudaError_t e = p.mode == 3 ? cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<true>, p)
+                              : cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<false>, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return fail(B200_LORA_ECUDA, "bgmv_fused_kernel launch: %s", cudaGetErrorString(e));
