@@ -8,6 +8,7 @@ launch function without a CUDA device raises.  The C declarations live in
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 from ctypes import POINTER, c_char_p, c_float, c_int32, c_int64, c_size_t, c_void_p
@@ -167,19 +168,50 @@ def ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+_PTR_ARRAYS: dict[tuple, ctypes.Array] = {}
+_INT_ARRAYS: dict[tuple, ctypes.Array] = {}
+
+
 def ptr_array(tensors) -> ctypes.Array:
-    arr = (c_void_p * len(tensors))()
-    for i, t in enumerate(tensors):
-        arr[i] = t.data_ptr() if t is not None else None
+    """Host array of device pointers; arrays are kept per pointer tuple (a layer passes the same slabs every call)."""
+    key = tuple(t.data_ptr() if t is not None else 0 for t in tensors)
+    arr = _PTR_ARRAYS.get(key)
+    if arr is None:
+        if len(_PTR_ARRAYS) > 4096:
+            _PTR_ARRAYS.clear()
+        arr = (c_void_p * len(key))(*[v or None for v in key])
+        _PTR_ARRAYS[key] = arr
     return arr
 
 
 def int_array(values) -> ctypes.Array:
-    return (c_int32 * len(values))(*[int(v) for v in values])
+    key = tuple(int(v) for v in values)
+    arr = _INT_ARRAYS.get(key)
+    if arr is None:
+        if len(_INT_ARRAYS) > 4096:
+            _INT_ARRAYS.clear()
+        arr = (c_int32 * len(key))(*key)
+        _INT_ARRAYS[key] = arr
+    return arr
+
+
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_NULL_CONTEXT = contextlib.nullcontext()
 
 
 def current_stream(device: torch.device) -> int:
+    """Raw ``cudaStream_t`` of torch's current stream on ``device`` (a few hundred nanoseconds)."""
+    if _RAW_STREAM is not None:
+        return _RAW_STREAM(device.index if device.index is not None else torch.cuda.current_device())
     return torch.cuda.current_stream(device).cuda_stream
+
+
+def on_device(device: torch.device):
+    """Context manager that makes ``device`` current; nothing happens when it already is (the usual case: the
+    full ``torch.cuda.device`` guard costs several microseconds per launch)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NULL_CONTEXT
+    return torch.cuda.device(device)
 
 
 def set_option(key: int, value: int) -> None:
@@ -205,10 +237,19 @@ def build_metadata(token_to_slot, S: int, convention: int, sorted_idx, slot_ids,
     if sorted_idx.numel() < T or counts.numel() < S + 1 or offsets.numel() < S + 2 or \
             (slot_ids is not None and slot_ids.numel() < S + 1) or (info is not None and info.numel() < 3):
         raise ValueError("metadata arrays are too small for T rows and S slots")
-    with torch.cuda.device(token_to_slot.device):
+    with on_device(token_to_slot.device):
         check(lib().lora_b200_build_metadata(ptr(token_to_slot), T, S, convention, ptr(sorted_idx), ptr(slot_ids),
                                              ptr(counts), ptr(offsets), ptr(info), current_stream(token_to_slot.device)))
 
 
+_WORKSPACE_BYTES: dict[tuple[int, int, int], int] = {}
+
+
 def workspace_bytes(T: int, n_slices: int, r_max: int) -> int:
-    return int(lib().lora_b200_workspace_bytes(T, n_slices, r_max))
+    key = (T, n_slices, r_max)
+    got = _WORKSPACE_BYTES.get(key)
+    if got is None:
+        if len(_WORKSPACE_BYTES) > 4096:
+            _WORKSPACE_BYTES.clear()
+        got = _WORKSPACE_BYTES[key] = int(lib().lora_b200_workspace_bytes(T, n_slices, r_max))
+    return got

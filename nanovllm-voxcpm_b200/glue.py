@@ -42,7 +42,7 @@ def add_rms_norm(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.T
         res2 = _rows(residual.reshape(-1, H), "residual")
         hidden = hidden_out if hidden_out is not None else torch.empty(T, H, dtype=x.dtype, device=x.device)
         hid2 = _rows(hidden.reshape(-1, H), "hidden_out")
-    with torch.cuda.device(x.device):
+    with N.on_device(x.device):
         N.check(N.lib().lora_b200_glue_add_rmsnorm(
             normed2.data_ptr(), normed2.stride(0), N.ptr(hid2), hid2.stride(0) if hid2 is not None else 0,
             x2.data_ptr(), x2.stride(0), N.ptr(res2), res2.stride(0) if res2 is not None else 0, weight.data_ptr(),
@@ -78,7 +78,7 @@ def silu_and_mul(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tens
     x2 = _rows(x.reshape(-1, shape[-1]), "x")
     res = out if out is not None else torch.empty(x2.size(0), inter, dtype=x.dtype, device=x.device)
     res2 = _rows(res.reshape(-1, inter), "out")
-    with torch.cuda.device(x.device):
+    with N.on_device(x.device):
         N.check(N.lib().lora_b200_glue_silu_mul(res2.data_ptr(), res2.stride(0), x2.data_ptr(), x2.stride(0), x2.size(0),
                                                 inter, N.dtype_code(x.dtype), N.current_stream(x.device)))
     return res2.view(*shape[:-1], inter)
@@ -127,7 +127,7 @@ def rope_kv_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim
         for c in (k_cache, v_cache):
             if not c.is_contiguous() or c.dtype != qkv.dtype or c.numel() % kv_size:
                 raise ValueError("the caches must be contiguous [..., kv_heads, head_dim] tensors of the dtype of qkv")
-    with torch.cuda.device(qkv.device):
+    with N.on_device(qkv.device):
         N.check(N.lib().lora_b200_glue_rope_kv_store(
             qkv2.data_ptr(), qkv2.stride(0), T, num_heads, num_kv_heads, head_dim, N.ptr(positions) if rope else None,
             N.ptr(cos) if rope else None, N.ptr(sin) if rope else None, table_dim, table_dtype, max_pos, N.ptr(k_cache),

@@ -170,7 +170,7 @@ def launch_add(
         impl == N.IMPL_SGMV or (impl == N.IMPL_AUTO and T >= SGMV_MIN_TOKENS)
     ):
         workspace = scratch_for(x.device, N.workspace_bytes(T, len(a_slabs), r_max))
-    with torch.cuda.device(x.device):
+    with N.on_device(x.device):
         rc = (N.lib().lora_b200_delta if overwrite else N.lib().lora_b200_add)(
             y_packed.data_ptr(), y_packed.stride(0), x.data_ptr(), x.stride(0), T, in_dim, len(a_slabs),
             N.ptr_array(a_slabs), N.ptr_array(b_slabs), N.int_array(out_sizes), N.int_array(col_offsets),
@@ -229,7 +229,7 @@ def linear_lora(
                 f"LoRA token_to_slot length does not match input rows: token_to_slot={token_to_slot.numel()} rows={T}"
             )
         workspace = scratch_for(x.device, N.workspace_bytes(T, n, r_max))
-    with torch.cuda.device(x.device):
+    with N.on_device(x.device):
         rc = N.lib().lora_b200_linear_lora(
             out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), T, in_dim, weight.data_ptr(), weight.stride(0),
             out_total, N.ptr(bias), n, N.ptr_array(a_slabs[:n]) if n else None, N.ptr_array(b_slabs[:n]) if n else None,
@@ -466,6 +466,6 @@ def prefetch_slabs(slabs, metadata: "LoRAMetadata") -> None:
     import ctypes
 
     strides = (ctypes.c_int64 * len(slabs))(*[t.stride(0) * t.element_size() for t in slabs])
-    with torch.cuda.device(ids.device):
+    with N.on_device(ids.device):
         N.check(N.lib().lora_b200_prefetch_slabs(N.ptr_array(slabs), strides, strides, len(slabs), ids.data_ptr(),
                                                  cnt.data_ptr(), n_buckets, S, N.current_stream(ids.device)))

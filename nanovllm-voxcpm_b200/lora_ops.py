@@ -45,7 +45,7 @@ def shrink_into(
         raise ValueError("lora_shrink input must be [tokens, in] with unit column stride")
     if token_lora_mapping.dtype != torch.int32 or token_lora_mapping.numel() < T:
         raise ValueError("token_lora_mapping must be int32 with one entry per token")
-    with torch.cuda.device(inputs.device):
+    with N.on_device(inputs.device):
         rc = N.lib().lora_b200_shrink(
             output_tensor.data_ptr(), N.dtype_code(output_tensor.dtype), inputs.data_ptr(), inputs.stride(0), T,
             in_dim, len(slabs), N.ptr_array(slabs), S, r, token_lora_mapping.data_ptr(), float(scaling),
@@ -79,7 +79,7 @@ def expand_into(
         cols.append(cols[-1] + w)
     if cols[-1] + widths[-1] > output_tensor.size(1):
         raise ValueError("lora_expand slices exceed the output width")
-    with torch.cuda.device(output_tensor.device):
+    with N.on_device(output_tensor.device):
         rc = N.lib().lora_b200_expand(
             output_tensor.data_ptr(), output_tensor.stride(0), inputs.data_ptr(), N.dtype_code(inputs.dtype), T,
             len(slabs), N.ptr_array(slabs), N.int_array(widths), N.int_array(cols), S, r,

@@ -200,7 +200,7 @@ class SlotLoader:
             n = src.numel() * src.element_size()
             host[table_bytes + off: table_bytes + off + n].copy_(src.view(torch.uint8).reshape(-1))
         total = table_bytes + plan.blob_bytes
-        with torch.cuda.device(self.device):
+        with N.on_device(self.device):
             dev[:total].copy_(host[:total], non_blocking=True)
             if arena_bytes:
                 # asynchronous when the arena is pinned; the payload must stay unchanged until the copy has run

@@ -42,7 +42,7 @@ class TpExchange:
         N.require_cuda(partial)
         if partial.dtype != torch.float32 or not partial.is_contiguous():
             raise ValueError("the exchanged partial must be a contiguous float32 tensor")
-        with torch.cuda.device(partial.device):
+        with N.on_device(partial.device):
             N.check(N.lib().lora_b200_tp_allreduce(partial.data_ptr(), partial.data_ptr(), partial.numel(), self._peers,
                                                    self.rank, self.tp, self.capacity, N.current_stream(partial.device)))
         return partial
@@ -85,7 +85,7 @@ def shrink_allreduce_expand(y, x, a_slabs, b_slabs, out_sizes, col_offsets, meta
         n_buckets = 0
     tmp = scratch_for(x.device, n * T * r_max * 4 + 256)
     tmp_ptr = (tmp.data_ptr() + 255) & ~255
-    with torch.cuda.device(x.device):
+    with N.on_device(x.device):
         N.check(N.lib().lora_b200_shrink_allreduce_expand(
             y.data_ptr(), y.stride(0), x.data_ptr(), x.stride(0), T, in_dim, n, N.ptr_array(a_slabs), N.ptr_array(b_slabs),
             N.int_array(out_sizes), N.int_array(col_offsets), S, r_max, N.ptr(_i32(rank_per_slot, "rank_per_slot")),
