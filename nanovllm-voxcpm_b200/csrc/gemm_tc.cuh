@@ -49,6 +49,12 @@ struct GemmArgs {
   int expand_mode;                 // 0 = LINEAR (store), 1 = EXPAND (reduce-add, blocks without -1 rows)
   int lora;                        // LINEAR: add the LoRA stages
   int overwrite;                   // EXPAND: store the delta tiles (-0.0 in rows without adapter) instead of adding them
+  // Programmatic dependent launch: the kernel may start while the previous kernel of the stream still runs.
+  // 1 = that kernel is this library's shrink (launched the ordinary way, so everything before it is complete, and
+  //     it writes nothing but tmp): only the first load of tmp waits for it; the set-up, and in LINEAR mode the base
+  //     GEMM of the first tiles, overlap it.
+  // 0 = unknown predecessor: the first load of anything waits.
+  int after_shrink;
 };
 
 struct GemmMaps {
@@ -198,6 +204,8 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
       tma_prefetch_desc(&maps.x); tma_prefetch_desc(&maps.w); tma_prefetch_desc(&maps.t); tma_prefetch_desc(&maps.y);
       const uint64_t w_policy = l2_policy_evict_last();
       int st = 0, round = 0;
+      bool waited = false;
+      if (!a.after_shrink) { griddep_wait(); waited = true; }
       for (int sg = 0; sg < nseg; ++sg) {
       int blk, ja, jb, nruns;
       seg_range(sg, blk, ja, jb, nruns);
@@ -216,6 +224,7 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
             const int lo = max(a.col[s], j * kSgmvBN), hi = min(a.col[s] + a.out[s], (j + 1) * kSgmvBN);
             if (lo >= hi) continue;
             if (round > 0) mbar_wait_bounded(empty_bar(st), (uint32_t)((round & 1) ^ 1), &abort_flag);
+            if (!waited) { griddep_wait(); waited = true; }  // tmp is final from here on
             const uint32_t base = smem_base + (uint32_t)st * kGemmStageBytes;
             mbar_arrive_expect_tx(full_bar(st), t_tile_bytes + b_tile_bytes);
             tma_load_2d(base, &maps.t, 0, s * a.T + blk * kSgmvBM, full_bar(st));
@@ -431,6 +440,7 @@ inline int tc_tile_prepare(const SgmvMaps& sm, const SgmvArgs& sa, const void* w
   a.expand_mode = expand_mode ? 1 : 0;
   a.lora = lora ? 1 : 0;
   a.overwrite = overwrite ? 1 : 0;
+  a.after_shrink = lora ? 1 : 0;  // every caller that asks for the LoRA stages has just launched the shrink
   maps->x = sm.x; maps->t = sm.t;
   for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) maps->b[s] = sm.b[s];
   maps->w = sm.x;
@@ -454,8 +464,22 @@ inline int tc_tile_launch(const GemmMaps& maps, const GemmArgs& a, cudaStream_t 
   int ncta = std::min(kTileSMs, total);
   const int max_per = (kTileMaxSeg - 1) * ntile;
   if ((total + ncta - 1) / ncta > max_per) ncta = (total + max_per - 1) / max_per;
-  tc_tile_kernel<<<ncta, kTileThreads, smem, stream>>>(maps, a);
-  return check_launch("tc_tile_kernel");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)ncta, 1, 1);
+  cfg.blockDim = dim3(kTileThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, tc_tile_kernel, maps, a);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(B200_LORA_ECUDA, "tc_tile_kernel launch: %s", cudaGetErrorString(e));
+  }
+  return B200_LORA_OK;
 }
 
 // y += LoRA delta for a prefill batch: shrink, then the reduce-add tile kernel (or the run-based

@@ -22,7 +22,7 @@ constexpr int kSgmvBM = 128;        // rows per block / MMA M
 constexpr int kShrinkRows = 64;     // rows of x one shrink CTA owns (the upper half of its M = 128 tiles is idle)
 constexpr int kSgmvBK = 64;         // K columns per shrink stage (one 128-byte swizzle row)
 constexpr int kSgmvBN = 256;        // output columns per expand tile
-constexpr int kSgmvShrinkMaxStages = 8;  // the launch picks as many 64-column stages as fit into shared memory
+constexpr int kSgmvShrinkMaxStages = 12; // the launch picks as many 64-column stages as fit into shared memory
 constexpr int kSgmvExpandStages = 3;
 constexpr int kSgmvAutoMinTokens = 512;  // IMPL_AUTO uses these kernels from this batch size on
 
@@ -121,6 +121,8 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
   const int blk = blockIdx.x;
   const int r = a.r_max, n = a.n;
   B200_SHRINK_TRACE_CTA(0)
+  // the tile kernel that follows may set itself up now; it waits for this kernel before it reads tmp
+  griddep_launch_dependents();
   // A CTA owns kShrinkRows = 64 rows of x: twice as many CTAs as 128-row blocks, so that most SMs of the GPU
   // stream x (a CTA's rate is bound by the bytes its ring keeps in flight). The MMAs stay M = 128: the x slot of a
   // stage has room for 128 rows, TMA fills the lower 64, the upper 64 hold stale bytes whose accumulator rows
