@@ -136,6 +136,9 @@ tc_tile_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int r = a.r_max, n = a.n;
   B200_TILE_TRACE_CTA(0)
+  // the next kernel of the stream, if it was launched as a programmatic dependent (this library's shrink and decode
+  // kernels are), may set itself up now; those kernels wait for this one before they touch activations or scratch
+  griddep_launch_dependents();
   // Persistent schedule: the output tiles, numbered row block major (id = blk * ntile_all + j), are
   // dealt to the CTAs in equal contiguous ranges, so every SM gets the same number of tiles and a CTA
   // changes row block at most kTileMaxSeg - 1 times.

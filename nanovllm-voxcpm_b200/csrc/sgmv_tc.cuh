@@ -121,8 +121,6 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
   const int blk = blockIdx.x;
   const int r = a.r_max, n = a.n;
   B200_SHRINK_TRACE_CTA(0)
-  // the tile kernel that follows may set itself up now; it waits for this kernel before it reads tmp
-  griddep_launch_dependents();
   // A CTA owns kShrinkRows = 64 rows of x: twice as many CTAs as 128-row blocks, so that most SMs of the GPU
   // stream x (a CTA's rate is bound by the bytes its ring keeps in flight). The MMAs stay M = 128: the x slot of a
   // stage has room for 128 rows, TMA fills the lower 64, the upper 64 hold stale bytes whose accumulator rows
@@ -151,6 +149,12 @@ sgmv_shrink_kernel(const __grid_constant__ SgmvMaps maps, const SgmvArgs a) {
     tc_fence_before_sync();
   }
   sgmv_find_runs<int, int, kShrinkRows>(a.token_to_slot, a.T, a.S, blk, s_slot, run_slot, run_lo, run_hi, &nruns_s);  // has __syncthreads
+  // Launched under programmatic dependent launch: everything above (barriers, TMEM, the run table from the index
+  // metadata) may overlap the previous kernel of the stream; x is read and tmp written only from here on.
+  griddep_wait();
+  // Only now may the tile kernel that follows start: it reads x (and W) without waiting for anything, so it must
+  // not run before the kernels ahead of this one are complete; it waits for this kernel before it reads tmp.
+  griddep_launch_dependents();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
   const int nruns = nruns_s;
@@ -482,8 +486,22 @@ inline int sgmv_launch_shrink(const SgmvMaps& maps, const SgmvArgs& a_in, cudaSt
   const size_t smem = ring + 1024;
   if (int rc = sgmv_set_smem(reinterpret_cast<const void*>(sgmv_shrink_kernel), smem)) return rc;
   const int nblk = (a.T + kShrinkRows - 1) / kShrinkRows;
-  sgmv_shrink_kernel<<<nblk, kSgmvThreads, smem, stream>>>(maps, a);
-  return check_launch("sgmv_shrink_kernel");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)nblk, 1, 1);
+  cfg.blockDim = dim3(kSgmvThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, sgmv_shrink_kernel, maps, a);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(B200_LORA_ECUDA, "sgmv_shrink_kernel launch: %s", cudaGetErrorString(e));
+  }
+  return B200_LORA_OK;
 }
 
 inline int sgmv_launch_expand(const SgmvMaps& maps, const SgmvArgs& a, cudaStream_t stream) {
