@@ -138,6 +138,24 @@ __device__ __forceinline__ float table_at(const void* tab, int dtype, int64_t id
   return __half2float(static_cast<const __half*>(tab)[idx]);
 }
 
+__device__ __forceinline__ void table_load8(const void* tab, int dtype, int64_t idx, float (&out)[8]) {
+  if (dtype == B200_LORA_F32) {
+    const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(tab) + idx);
+    const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(tab) + idx + 4);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+  } else if (dtype == B200_LORA_BF16) {
+    Vec8<__nv_bfloat16> v;
+    v.raw = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(tab) + idx);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) out[e] = v.get(e);
+  } else {
+    Vec8<__half> v;
+    v.raw = *reinterpret_cast<const uint4*>(static_cast<const __half*>(tab) + idx);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) out[e] = v.get(e);
+  }
+}
+
 // Work items of 16 bytes, flat over (token, item): a rotation item is (head, 8 adjacent columns j..j+7 of the
 // first half) -> y[j] = x[j] * cos[j] - x[j + D/2] * sin[j], y[j + D/2] = x[j + D/2] * cos[j + D/2] + x[j] * sin[j + D/2],
 // each product and the sum rounded separately in fp32 as the reference's elementwise chain does; a rotated k
@@ -169,14 +187,20 @@ __global__ void __launch_bounds__(kRopeThreads) rope_kv_store_kernel(const RopeK
       Vec8<T> lo, hi, olo, ohi;
       lo.raw = *reinterpret_cast<const uint4*>(h + j);
       hi.raw = *reinterpret_cast<const uint4*>(h + half + j);
+      // 8 consecutive table entries per operand, fetched as 16-byte vectors (tb is a multiple of 8 entries)
+      float c1[8], s1[8], c2[8], s2[8];
+      table_load8(p.cos, p.table_dtype, tb, c1);
+      table_load8(p.sin, p.table_dtype, tb, s1);
+      if (hi_off) {
+        table_load8(p.cos, p.table_dtype, tb + hi_off, c2);
+        table_load8(p.sin, p.table_dtype, tb + hi_off, s2);
+      }
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const float x1 = lo.get(e), x2 = hi.get(e);
-        const float c1 = table_at(p.cos, p.table_dtype, tb + e), s1 = table_at(p.sin, p.table_dtype, tb + e);
-        const float c2 = hi_off ? table_at(p.cos, p.table_dtype, tb + hi_off + e) : c1;
-        const float s2 = hi_off ? table_at(p.sin, p.table_dtype, tb + hi_off + e) : s1;
-        olo.set(e, __fadd_rn(__fmul_rn(x1, c1), __fmul_rn(-x2, s1)));
-        ohi.set(e, __fadd_rn(__fmul_rn(x2, c2), __fmul_rn(x1, s2)));
+        const float cc2 = hi_off ? c2[e] : c1[e], ss2 = hi_off ? s2[e] : s1[e];
+        olo.set(e, __fadd_rn(__fmul_rn(x1, c1[e]), __fmul_rn(-x2, s1[e])));
+        ohi.set(e, __fadd_rn(__fmul_rn(x2, cc2), __fmul_rn(x1, ss2)));
       }
       *reinterpret_cast<uint4*>(h + j) = olo.raw;
       *reinterpret_cast<uint4*>(h + half + j) = ohi.raw;
