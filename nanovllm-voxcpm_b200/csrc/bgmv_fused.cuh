@@ -46,6 +46,7 @@ constexpr int kBgmvKP = 1024;          // columns per shrink tile
 constexpr int kBgmvXBlocks = kBgmvKP / 32 / kBgmvWarps;  // 32-column blocks per warp and tile
 constexpr int kBgmvSmemMax = 232448;   // 227 KB opt-in maximum per CTA
 constexpr int kBgmvMaxStages = 12;
+constexpr int kBgmvMaxExpandTiles = 256;  // expand tiles of one CTA (entries of its tile table)
 
 // status bits of the device status word
 constexpr int kStatusWaitGaveUp = 1;
@@ -96,7 +97,8 @@ struct BgmvParams {
   int red_pitch;    // floats per token row of the cross-warp reduction buffer
   int pitchT;       // bytes per token row of tmp
   int tmp_bytes;    // bytes of one tmp buffer
-  int off_red, off_tmp, off_bar;
+  int off_red, off_tmp, off_tab, off_bar;
+  int full_k;       // every K part has all 1024 columns
   int use_pdl;
   int mode;         // 0 fused, 1 shrink only (tmp_io written), 2 expand only (tmp_io read), 3 overwrite y
   float* tmp_io;
@@ -125,14 +127,14 @@ __device__ __forceinline__ void bgmv_fill_rows_without_delta(const BgmvParams& p
   }
 }
 
+// Two CTAs per SM: the CTAs of the next launch of the stream become resident while this launch still
+// runs, so their weight copies and L2 prefetches overlap this launch's dependent chain.
 #ifndef BGMV_MINBLOCKS
-#define BGMV_MINBLOCKS 1
+#define BGMV_MINBLOCKS 2
 #endif
-#ifndef BGMV_YDEPTH
-#define BGMV_YDEPTH 2
-#endif
-// kOverwrite = mode 3, compiled separately so that the add path carries none of its branches
-template <bool kOverwrite>
+// kOverwrite = mode 3, compiled separately so that the add path carries none of its branches;
+// kFullK = every K part has all 1024 columns (in_dim a multiple of 1024): no column checks in the shrink
+template <bool kOverwrite, bool kFullK>
 __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kernel(const __grid_constant__ BgmvParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -165,8 +167,8 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
     mbar_init(full_bar(tid), 1);
     mbar_init(empty_bar(tid), kBgmvWarps);
     if (tid == 0) {
-      mbar_init(tmp_ready_bars, (uint32_t)C);
-      mbar_init(tmp_ready_bars + 8u, (uint32_t)C);
+      mbar_init(tmp_ready_bars, 1u);  // completed by byte count (st.async from every CTA of the cluster)
+      mbar_init(tmp_ready_bars + 8u, 1u);
       *abort_flag = 0;
     }
     mbar_fence_init();
@@ -176,10 +178,12 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
   if (p.rank_per_slot != nullptr && slot >= 0 && slot < p.S) rank = min(max(p.rank_per_slot[slot], 0), p.r_max);
   const int r_eff = min(p.r_max, (rank + 31) & ~31);
   if (slot < 0 || slot >= p.S || cnt <= 0 || start < 0 || start > p.T - cnt || r_eff == 0) {
-    if (kOverwrite) {  // an idle cluster still does its share of the -0.0 rows
-      if (p.use_pdl) griddep_wait();
+    // An idle cluster holds nothing, but one CTA of every launch must outlive the previous launch
+    // of the stream: a launch that ended before its predecessor would let the launch behind it
+    // pass its own wait too early.
+    if (p.use_pdl && (kOverwrite || (bucket == 0 && c == 0))) griddep_wait();
+    if (kOverwrite)  // an idle cluster still does its share of the -0.0 rows
       bgmv_fill_rows_without_delta(p, bucket * C + c, (int)gridDim.y * C, tid, kBgmvThreads);
-    }
     return;
   }
   const float sc = p.scaling * (p.scale_per_slot != nullptr ? p.scale_per_slot[slot] : 1.0f);
@@ -210,6 +214,12 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
   }
   const int npass = (cnt + kBgmvTok - 1) >> 4;
   const int total = (shrink_tiles + tiles_exp) * npass;
+  // bytes a pass delivers into this CTA's tmp buffer: 16 token rows of all Q stacked rank rows
+  const uint32_t gather_bytes = (uint32_t)(kBgmvTok * Q * 2);
+  if (tid == 0 && (mode == 0 || mode == 3)) {
+    mbar_arrive_expect_tx(tmp_ready_bars, gather_bytes);                      // pass 0
+    if (npass > 1) mbar_arrive_expect_tx(tmp_ready_bars + 8u, gather_bytes);  // pass 1
+  }
 
   __syncthreads();  // barriers initialised
   B200_TRACE_POINT(2)
@@ -291,6 +301,28 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
       if (++p_stage == NS) { p_stage = 0; ++p_round; }
       if (it + 1 == npro) {
         B200_TRACE_PRODUCER(3)
+        // The ring is full and the previous launch of the stream may still be running: ask the L2 for
+        // the rest of this CTA's weights now, so that the refills that follow the wait find them there.
+        if (shrink_tiles + tiles_exp > npro && lane == 0) {
+          int q = q_lo;
+          const int q_hi = q_lo + rows_c;
+          while (q < q_hi) {
+            const int s = q / r_eff, r0 = q - s * r_eff;
+            const int nr = min(r_eff - r0, q_hi - q);
+            const void* aptr = nullptr;
+#pragma unroll
+            for (int ss = 0; ss < B200_LORA_MAX_SLICES; ++ss)
+              if (ss == s) aptr = p.st.a[ss];
+            bulk_prefetch_l2(static_cast<const __nv_bfloat16*>(aptr) + ((int64_t)slot * p.r_max + r0) * in_dim,
+                             (uint32_t)nr * (uint32_t)in_dim * 2u);
+            q += nr;
+          }
+#pragma unroll
+          for (int s = 0; s < B200_LORA_MAX_SLICES; ++s)
+            if (s < n && e_n[s] > 0)
+              bulk_prefetch_l2(static_cast<const __nv_bfloat16*>(p.st.b[s]) + ((int64_t)slot * p.st.out[s] + e_lo[s]) * p.r_max,
+                               (uint32_t)e_n[s] * (uint32_t)p.r_max * 2u);
+        }
       }
     }
     cluster_wait();
@@ -298,90 +330,95 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
   }
 
   // ============================= consumer warps =============================
-  // Token rows of the first pass (index metadata: safe before the wait). While the previous
-  // kernel finishes, pull this CTA's activation rows and its first output columns into L2:
-  // a prefetch never creates stale data (L2 is the point of coherence), it only hides the
-  // HBM latency of rows nobody has touched recently.
+  // Everything that does not depend on the previous launch of the stream is done before the wait:
+  // token rows, the table of this CTA's expand tiles, thread-constant address pieces and L2 prefetches
+  // (a prefetch never creates stale data: L2 is the point of coherence). What runs after the wait is
+  // the dependent chain activations -> shrink -> all-gather -> expand, kept as short as possible.
   int tok0_lo = -1, tok0_hi = -1;
   if (g < cnt) tok0_lo = p.sorted_idx[start + g];
   if (g + 8 < cnt) tok0_hi = p.sorted_idx[start + g + 8];
   if (tok0_lo >= p.T) tok0_lo = -1;
   if (tok0_hi >= p.T) tok0_hi = -1;
+
+  // expand tile e of this CTA (ring order): x = first y column, y = rows | slice << 16
+  int2* etab = reinterpret_cast<int2*>(smem + p.off_tab);
+  for (int e = tid; e < tiles_exp; e += kBgmvConsumers) {
+    int s_e = 0, et = e;
+#pragma unroll
+    for (int s = 0; s < B200_LORA_MAX_SLICES - 1; ++s)
+      if (s_e == s && et >= e_tiles[s]) { et -= e_tiles[s]; s_e = s + 1; }
+    int lo = 0, en = 0, cb = 0;
+#pragma unroll
+    for (int s = 0; s < B200_LORA_MAX_SLICES; ++s)
+      if (s == s_e) { lo = e_lo[s]; en = e_n[s]; cb = p.st.col[s]; }
+    const int r0 = et << p.er_shift;
+    etab[e] = make_int2(cb + lo + r0, min(ER, en - r0) | (s_e << 16));
+  }
+  named_bar_sync(1, kBgmvConsumers);  // table complete
+
+  const int rb = warp * 32;             // expand: out rows of this warp inside a tile
+  const int x_col = warp * 32 + t * 8;  // shrink: first column of the thread inside a K part (block i adds 256)
+  const int y_col = rb + 8 * t;         // expand: first of the thread's 8 output columns inside a tile
   if (p.use_pdl) {
     if (rows_c > 0) {
-      for (int kc = warp * 32 + t * 8; kc < in_dim; kc += kBgmvWarps * 32) {
+      for (int kc = x_col; kc < in_dim; kc += kBgmvWarps * 32) {
         if (tok0_lo >= 0) prefetch_l2(p.x + (int64_t)tok0_lo * p.x_ld + kc);
         if (tok0_hi >= 0) prefetch_l2(p.x + (int64_t)tok0_hi * p.x_ld + kc);
       }
     }
-#pragma unroll
-    for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) {
-      if (s < n && !kOverwrite) {
-        for (int r = warp * 32 + t * 8; r < e_n[s]; r += kBgmvWarps * 32) {
-          const int cc = p.st.col[s] + e_lo[s] + r;
-          if (tok0_lo >= 0) prefetch_l2(p.y + (int64_t)tok0_lo * p.y_ld + cc);
-          if (tok0_hi >= 0) prefetch_l2(p.y + (int64_t)tok0_hi * p.y_ld + cc);
+    if (!kOverwrite) {  // the lines of y that this thread's reductions will land in
+      for (int e = 0; e < tiles_exp; ++e) {
+        const int2 te = etab[e];
+        if (y_col < (te.y & 0xffff)) {
+          if (tok0_lo >= 0) prefetch_l2(p.y + (int64_t)tok0_lo * p.y_ld + te.x + y_col);
+          if (tok0_hi >= 0) prefetch_l2(p.y + (int64_t)tok0_hi * p.y_ld + te.x + y_col);
         }
       }
     }
-    griddep_wait();  // x and y of this launch are final from here on
   }
+
+  // thread-constant pieces of the shared-memory addresses
+  const uint32_t pitchB = (uint32_t)p.r_max * 2u;
+  const uint32_t a_off = (uint32_t)(g * pitchA + x_col * 2);                            // shrink tile: row g
+  const uint32_t w_off = (uint32_t)(rb + 8 * (g >> 1) + (g & 1)) * pitchB + (uint32_t)t * 16u;  // expand tile
+  // MMA column n of n-tile j reads slab row 8*(n/2) + 2j + (n%2) of the warp's 32 rows: thread (g,t)
+  // then owns 8 consecutive output columns 8t..8t+7 of the block.
+  const uint32_t t_off = (uint32_t)(g * p.pitchT + t * 16);                             // tmp: token row g
+  float* const red_wr = red + ((size_t)warp * kBgmvTok + g) * p.red_pitch + 2 * t;      // + 8 * pitch: token g + 8
+  const int kblocks = r_eff >> 5;
+  // all-gather item of this thread: one token row x four consecutive rank rows of this CTA
+  const int groups = rows_c >> 2;
+  const bool has_item = tid < kBgmvTok * groups;
+  const int it_tok = has_item ? tid / groups : 0;
+  const int it_q = q_lo + 4 * (has_item ? tid - it_tok * groups : 0);
+  const float* const red_rd = red + (size_t)it_tok * p.red_pitch + (it_q - q_lo);
+  const uint32_t it_off = (uint32_t)(it_tok * p.pitchT + it_q * 2);
+  const uint32_t tmp_u32 = smem_u32(tmp_base);
+
+  if (p.use_pdl) griddep_wait();  // x and y of this launch are final from here on
   if (kOverwrite) bgmv_fill_rows_without_delta(p, bucket * C + c, (int)gridDim.y * C, tid, kBgmvConsumers);
   B200_TRACE_POINT(4)
 
-  int c_stage = 0, c_round = 0;  // stage / round of the tile being consumed
+  int c_stage = 0;
+  uint32_t c_parity = 0, stage_addr = ring_base;  // stage being consumed: index, phase, address
   auto advance = [&]() {
-    if (++c_stage == NS) { c_stage = 0; ++c_round; }
+    stage_addr += (uint32_t)p.stage_bytes;
+    if (++c_stage == NS) { c_stage = 0; c_parity ^= 1u; stage_addr = ring_base; }
   };
-  const uint32_t pitchB = (uint32_t)p.r_max * 2u;
-  const int kblocks = r_eff >> 5;
 
   for (int pass = 0; pass < npass; ++pass) {
-    const bool valid_lo = pass * kBgmvTok + g < cnt;
-    const bool valid_hi = pass * kBgmvTok + g + 8 < cnt;
     int tok_lo = tok0_lo, tok_hi = tok0_hi;
     if (pass > 0) {
       tok_lo = tok_hi = -1;
-      if (valid_lo) tok_lo = p.sorted_idx[start + pass * kBgmvTok + g];
-      if (valid_hi) tok_hi = p.sorted_idx[start + pass * kBgmvTok + g + 8];
+      if (pass * kBgmvTok + g < cnt) tok_lo = p.sorted_idx[start + pass * kBgmvTok + g];
+      if (pass * kBgmvTok + g + 8 < cnt) tok_hi = p.sorted_idx[start + pass * kBgmvTok + g + 8];
       if (tok_lo >= p.T) tok_lo = -1;
       if (tok_hi >= p.T) tok_hi = -1;
     }
-
-    // y of this CTA's expand tiles is requested two tiles ahead (the first two right here, before
-    // the shrink), so the read-modify-write of y never waits for an L2 round trip.
-    int ys = 0, yet = 0, yleft = tiles_exp;  // cursor of the next tile whose y gets requested
-    auto y_next = [&](uint4& lo4, uint4& hi4, int& col_, int& nrows_, int& s_) {
-      lo4 = hi4 = make_uint4(0, 0, 0, 0);
-      col_ = 0; nrows_ = 0; s_ = 0;
-      if (yleft <= 0) return;
-      --yleft;
-#pragma unroll
-      for (int s = 0; s < B200_LORA_MAX_SLICES - 1; ++s)  // skip slices this CTA has no tiles of
-        if (ys == s && yet >= e_tiles[s]) { ys = s + 1; yet = 0; }
-      int lo = 0, en = 0, cb = 0;
-#pragma unroll
-      for (int s = 0; s < B200_LORA_MAX_SLICES; ++s)
-        if (s == ys) { lo = e_lo[s]; en = e_n[s]; cb = p.st.col[s]; }
-      const int r0 = yet << p.er_shift;
-      nrows_ = min(ER, en - r0);
-      col_ = cb + lo + r0;
-      s_ = ys;
-      ++yet;
-      if (!kOverwrite && warp * 32 + 8 * t < nrows_) {  // (overwrite: y is not read, the delta is added to zeros)
-        const int cc = col_ + warp * 32 + 8 * t;
-        if (tok_lo >= 0) lo4 = ldg128(p.y + (int64_t)tok_lo * p.y_ld + cc);
-        if (tok_hi >= 0) hi4 = ldg128(p.y + (int64_t)tok_hi * p.y_ld + cc);
-      }
-    };
-    uint4 q0lo, q0hi, q1lo, q1hi;
-    int q0col, q0rows, q0s, q1col, q1rows, q1s;
-    y_next(q0lo, q0hi, q0col, q0rows, q0s);
-#if BGMV_YDEPTH == 2
-    y_next(q1lo, q1hi, q1col, q1rows, q1s);
-#else
-    q1lo = q1hi = make_uint4(0, 0, 0, 0); q1col = q1rows = q1s = 0;
-#endif
+    const __nv_bfloat16* const xlo_p = p.x + (int64_t)max(tok_lo, 0) * p.x_ld + x_col;
+    const __nv_bfloat16* const xhi_p = p.x + (int64_t)max(tok_hi, 0) * p.x_ld + x_col;
+    __nv_bfloat16* const ylo_p = p.y + (int64_t)max(tok_lo, 0) * p.y_ld + y_col;
+    __nv_bfloat16* const yhi_p = p.y + (int64_t)max(tok_hi, 0) * p.y_ld + y_col;
 
     // ===== shrink: red[warp][tok][row] = x[16 tok, K blocks of this warp] . A_rows^T =====
     for (int kp = 0; kp < (rows_c > 0 ? nkp : 0); ++kp) {
@@ -390,63 +427,62 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
       uint4 xlo[kBgmvXBlocks], xhi[kBgmvXBlocks];
 #pragma unroll
       for (int i = 0; i < kBgmvXBlocks; ++i) {
-        const int kl = (warp + kBgmvWarps * i) * 32;
-        const int kcol = k0 + kl + t * 8;
         xlo[i] = xhi[i] = make_uint4(0, 0, 0, 0);
-        if (kl < KP && kcol < in_dim) {
-          if (tok_lo >= 0) xlo[i] = ldg128_nc(p.x + (int64_t)tok_lo * p.x_ld + kcol);
-          if (tok_hi >= 0) xhi[i] = ldg128_nc(p.x + (int64_t)tok_hi * p.x_ld + kcol);
+        if (kFullK || (x_col + 256 * i < KP && k0 + x_col + 256 * i < in_dim)) {
+          if (tok_lo >= 0) xlo[i] = ldg128_nc(xlo_p + k0 + 256 * i);
+          if (tok_hi >= 0) xhi[i] = ldg128_nc(xhi_p + k0 + 256 * i);
         }
       }
       for (int j = 0; j < nt_c; ++j) {
-        mbar_wait_bounded(full_bar(c_stage), (uint32_t)(c_round & 1), abort_flag);
+        mbar_wait_bounded(full_bar(c_stage), c_parity, abort_flag);
         if (kp == 0 && j == 0 && pass == 0) { B200_TRACE_POINT(5) }
-        const uint32_t sbase = ring_base + (uint32_t)c_stage * (uint32_t)p.stage_bytes;
         // two independent accumulator chains halve the dependent-MMA latency
         float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
         uint4 w[kBgmvXBlocks];
 #pragma unroll
         for (int i = 0; i < kBgmvXBlocks; ++i) {
-          const int kl = (warp + kBgmvWarps * i) * 32;
           w[i] = make_uint4(0, 0, 0, 0);
-          if (kl < KP && k0 + kl < in_dim) w[i] = lds128(sbase + (uint32_t)(g * pitchA) + (uint32_t)(kl + t * 8) * 2u);
+          if (kFullK || (x_col + 256 * i < KP && k0 + x_col + 256 * i < in_dim)) w[i] = lds128(stage_addr + a_off + 512u * i);
         }
 #pragma unroll
         for (int i = 0; i < kBgmvXBlocks; ++i) {
           mma_bf16_16816(acc, xlo[i].x, xhi[i].x, xlo[i].y, xhi[i].y, w[i].x, w[i].y);
           mma_bf16_16816(acc2, xlo[i].z, xhi[i].z, xlo[i].w, xhi[i].w, w[i].z, w[i].w);
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[i] += acc2[i];
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(c_stage));
         advance();
         // acc holds (tok g | g+8, rank rows 8j+2t, 8j+2t+1): accumulate over K parts per warp
-        float2* r0 = reinterpret_cast<float2*>(red + ((size_t)warp * kBgmvTok + g) * p.red_pitch + 8 * j + 2 * t);
-        float2* r1 = reinterpret_cast<float2*>(red + ((size_t)warp * kBgmvTok + g + 8) * p.red_pitch + 8 * j + 2 * t);
+        float2* r0 = reinterpret_cast<float2*>(red_wr + 8 * j);
+        float2* r1 = reinterpret_cast<float2*>(red_wr + 8 * p.red_pitch + 8 * j);
         if (kp == 0) {
-          *r0 = make_float2(acc[0], acc[1]);
-          *r1 = make_float2(acc[2], acc[3]);
+          *r0 = make_float2(acc[0] + acc2[0], acc[1] + acc2[1]);
+          *r1 = make_float2(acc[2] + acc2[2], acc[3] + acc2[3]);
         } else {
           const float2 a = *r0, b = *r1;
-          *r0 = make_float2(a.x + acc[0], a.y + acc[1]);
-          *r1 = make_float2(b.x + acc[2], b.y + acc[3]);
+          *r0 = make_float2(a.x + acc[0] + acc2[0], a.y + acc[1] + acc2[1]);
+          *r1 = make_float2(b.x + acc[2] + acc2[2], b.y + acc[3] + acc2[3]);
         }
       }
     }
     if (pass == 0) { B200_TRACE_POINT(6) }
 
     // ===== cross-warp reduction of the K slices, scale, bf16, all-gather =====
+    // the barrier of pass + 1 is armed one pass ahead (passes 0 and 1 at start-up): every local wait on
+    // its previous phase is over, and no peer sends for pass + 1 before it has this pass from this CTA
+    if (tid == 0 && pass >= 1 && pass + 1 < npass && (mode == 0 || mode == 3))
+      mbar_arrive_expect_tx(tmp_ready_bars + 8u * (uint32_t)((pass + 1) & 1), gather_bytes);
     named_bar_sync(1, kBgmvConsumers);
     if (pass == 0) {
       B200_TRACE_POINT(7)
       cluster_wait();  // start-up barrier: peers run and their barriers are initialised
     }
-    uint8_t* tmp_full = tmp_base + (size_t)(pass & 1) * p.tmp_bytes;
+    const uint32_t tmp_cur = tmp_u32 + (uint32_t)((pass & 1) * p.tmp_bytes);
     const uint32_t tmp_ready_bar = tmp_ready_bars + 8u * (uint32_t)(pass & 1);
     if (mode == 2) {
       // expand only: tmp of this pass comes from global memory (fp32 [n, T, r_max], summed over the
       // tensor-parallel ranks) and is rounded to bf16 into this CTA's own buffer
+      uint8_t* tmp_full = tmp_base + (size_t)(pass & 1) * p.tmp_bytes;
       const int tok = tid >> 4;
       int trow = -1;
       if (pass * kBgmvTok + tok < cnt) trow = p.sorted_idx[start + pass * kBgmvTok + tok];
@@ -459,78 +495,59 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
       }
       named_bar_sync(1, kBgmvConsumers);
     } else {
-      const int half = rows_c >> 1;
-      const int tok = tid >> 4;
-      int trow = -1;  // shrink only: token row of `tok`
-      if (mode == 1) {
-        if (pass * kBgmvTok + tok < cnt) trow = p.sorted_idx[start + pass * kBgmvTok + tok];
-        if (trow >= p.T) trow = -1;
-      }
-      for (int pr = tid & 15; pr < half; pr += 16) {
-        float s0 = 0.f, s1 = 0.f;
+      if (has_item) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int w = 0; w < kBgmvWarps; ++w) {
-          const float2 v = *reinterpret_cast<const float2*>(red + ((size_t)w * kBgmvTok + tok) * p.red_pitch + 2 * pr);
-          s0 += v.x;
-          s1 += v.y;
+          const float4 v = *reinterpret_cast<const float4*>(red_rd + (size_t)w * kBgmvTok * p.red_pitch);
+          a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
         }
         if (mode == 1) {
           // shrink only: fp32 result of this CTA's rank rows straight to global memory
-          const int q = q_lo + 2 * pr, s = q / r_eff, rr = q - s * r_eff;
-          if (trow >= 0)
-            *reinterpret_cast<float2*>(p.tmp_io + ((int64_t)s * p.T + trow) * p.r_max + rr) = make_float2(s0 * sc, s1 * sc);
+          int trow = -1;
+          if (pass * kBgmvTok + it_tok < cnt) trow = p.sorted_idx[start + pass * kBgmvTok + it_tok];
+          if (trow >= 0 && trow < p.T) {
+            const int s = it_q / r_eff, rr = it_q - s * r_eff;
+            float2* dst = reinterpret_cast<float2*>(p.tmp_io + ((int64_t)s * p.T + trow) * p.r_max + rr);
+            dst[0] = make_float2(a.x * sc, a.y * sc);
+            dst[1] = make_float2(a.z * sc, a.w * sc);
+          }
         } else {
-          const uint32_t v = pack_bf16x2(s0 * sc, s1 * sc);
-          const uint32_t laddr = smem_u32(tmp_full + (size_t)tok * p.pitchT + (size_t)(q_lo + 2 * pr) * 2);
-          for (int rc = 0; rc < C; ++rc) st_cluster_u32(mapa_shared(laddr, (uint32_t)rc), v);
+          // to every CTA of the cluster (this one included): 8 bytes of tmp + their count on the
+          // receiver's barrier in one operation
+          const uint32_t v0 = pack_bf16x2(a.x * sc, a.y * sc), v1 = pack_bf16x2(a.z * sc, a.w * sc);
+          for (int rc = 0; rc < C; ++rc)
+            st_async_b32x2(mapa_shared(tmp_cur + it_off, (uint32_t)rc), v0, v1, mapa_shared(tmp_ready_bar, (uint32_t)rc));
         }
       }
       if (mode == 1) {
         named_bar_sync(1, kBgmvConsumers);  // all warps have read the reduction buffer before the next pass refills it
         continue;
       }
-      named_bar_sync(1, kBgmvConsumers);  // every store of this CTA is issued
-      if (tid < C) mbar_arrive_remote_release(mapa_shared(tmp_ready_bar, (uint32_t)tid));
       if (pass == 0) { B200_TRACE_POINT(8) }
-
-      // ===== expand: y[tok, cols] += tmp[16 tok, r] . B_rows^T ======================
+      // (the wait also orders the reduction buffer: no warp passes it before every warp of every CTA
+      // of the cluster has summed and sent its items, so the next pass may refill the buffer)
       mbar_wait_bounded_acquire_cluster(tmp_ready_bar, (uint32_t)((pass >> 1) & 1), abort_flag);
       if (pass == 0) { B200_TRACE_POINT(9) }
     }
-    const uint32_t tmp_lo = smem_u32(tmp_full + (size_t)g * p.pitchT);
-    const uint32_t tmp_hi = smem_u32(tmp_full + (size_t)(g + 8) * p.pitchT);
 
+    // ===== expand: y[tok, cols] += tmp[16 tok, r] . B_rows^T ======================
     for (int e = 0; e < tiles_exp; ++e) {
-      // y of tile e was requested two tiles ago; request tile e+2 now
-      const uint4 ylo = q0lo, yhi = q0hi;
-      const int col = q0col, nrows = q0rows, s_cur = q0s;
-#if BGMV_YDEPTH == 2
-      q0lo = q1lo; q0hi = q1hi; q0col = q1col; q0rows = q1rows; q0s = q1s;
-      y_next(q1lo, q1hi, q1col, q1rows, q1s);
-#else
-      y_next(q0lo, q0hi, q0col, q0rows, q0s);
-#endif
-      mbar_wait_bounded(full_bar(c_stage), (uint32_t)(c_round & 1), abort_flag);
+      const int2 te = etab[e];
+      const int nrows = te.y & 0xffff;
+      const uint32_t a_addr = tmp_cur + t_off + (uint32_t)((te.y >> 16) * r_eff * 2);
+      mbar_wait_bounded(full_bar(c_stage), c_parity, abort_flag);
       if (pass == 0 && e < 5) { B200_TRACE_POINT(12 + 4 * e) }
-      const uint32_t sbase = ring_base + (uint32_t)c_stage * (uint32_t)p.stage_bytes;
-      const int rb = warp * 32;  // ER <= 256: one 32-row block per warp and tile
-      if (rb < nrows) {
+      if (rb < nrows) {  // ER <= 256: one 32-row block per warp and tile
         float d[4][4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.f;
         for (int kb = 0; kb < kblocks; ++kb) {
-          const uint32_t koff = (uint32_t)(s_cur * r_eff + kb * 32 + t * 8) * 2u;
-          const uint4 alo = lds128(tmp_lo + koff);
-          const uint4 ahi = lds128(tmp_hi + koff);
-          const uint32_t woff = (uint32_t)(kb * 32 + t * 8) * 2u;
+          const uint4 alo = lds128(a_addr + 64u * kb);
+          const uint4 ahi = lds128(a_addr + 8u * (uint32_t)p.pitchT + 64u * kb);
           uint4 w[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            // MMA column n of tile j reads slab row 8*(n/2) + 2j + (n%2): thread (g,t)
-            // then owns 8 consecutive output columns 8t..8t+7 of the block.
-            const int prow = rb + 8 * (g >> 1) + 2 * j + (g & 1);
-            w[j] = lds128(sbase + (uint32_t)prow * pitchB + woff);
-          }
+          for (int j = 0; j < 4; ++j) w[j] = lds128(stage_addr + w_off + 2u * j * pitchB + 64u * kb);
 #pragma unroll
           for (int j = 0; j < 4; ++j) mma_bf16_16816(d[j], alo.x, ahi.x, alo.y, ahi.y, w[j].x, w[j].y);
 #pragma unroll
@@ -539,23 +556,24 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(c_stage));  // the stage is in registers now
         if (pass == 0 && e < 5) { B200_TRACE_POINT(13 + 4 * e) }
-        if (rb + 8 * t < nrows) {
-          const int cc = col + rb + 8 * t;
-          if (tok_lo >= 0) {
-            uint4 v = ylo;
-            v.x = add_bf16x2(v.x, d[0][0], d[0][1]);
-            v.y = add_bf16x2(v.y, d[1][0], d[1][1]);
-            v.z = add_bf16x2(v.z, d[2][0], d[2][1]);
-            v.w = add_bf16x2(v.w, d[3][0], d[3][1]);
-            stg128(p.y + (int64_t)tok_lo * p.y_ld + cc, v);
-          }
-          if (tok_hi >= 0) {
-            uint4 v = yhi;
-            v.x = add_bf16x2(v.x, d[0][2], d[0][3]);
-            v.y = add_bf16x2(v.y, d[1][2], d[1][3]);
-            v.z = add_bf16x2(v.z, d[2][2], d[2][3]);
-            v.w = add_bf16x2(v.w, d[3][2], d[3][3]);
-            stg128(p.y + (int64_t)tok_hi * p.y_ld + cc, v);
+        if (y_col < nrows) {
+          if (kOverwrite) {
+            if (tok_lo >= 0)
+              stg128(ylo_p + te.x, make_uint4(pack_bf16x2(d[0][0], d[0][1]), pack_bf16x2(d[1][0], d[1][1]),
+                                              pack_bf16x2(d[2][0], d[2][1]), pack_bf16x2(d[3][0], d[3][1])));
+            if (tok_hi >= 0)
+              stg128(yhi_p + te.x, make_uint4(pack_bf16x2(d[0][2], d[0][3]), pack_bf16x2(d[1][2], d[1][3]),
+                                              pack_bf16x2(d[2][2], d[2][3]), pack_bf16x2(d[3][2], d[3][3])));
+          } else {
+            // The delta is rounded to bf16 and added to y by one 16-byte reduction at the L2: y never
+            // travels to the SM and nothing waits for it. Each element of y receives exactly one
+            // reduction per launch, so the result does not depend on their order.
+            if (tok_lo >= 0)
+              red_add_bf16x8(ylo_p + te.x, pack_bf16x2(d[0][0], d[0][1]), pack_bf16x2(d[1][0], d[1][1]),
+                             pack_bf16x2(d[2][0], d[2][1]), pack_bf16x2(d[3][0], d[3][1]));
+            if (tok_hi >= 0)
+              red_add_bf16x8(yhi_p + te.x, pack_bf16x2(d[0][2], d[0][3]), pack_bf16x2(d[1][2], d[1][3]),
+                             pack_bf16x2(d[2][2], d[2][3]), pack_bf16x2(d[3][2], d[3][3]));
           }
         }
       } else {
@@ -581,7 +599,9 @@ inline BgmvOptions& bgmv_options() {
   static BgmvOptions o;
   return o;
 }
-constexpr int kBgmvDefaultRingKb = 200;  // as many tiles in flight as fit (measured best on B200)
+// Default budget of one CTA: half of an SM's shared memory (228 KB minus 1 KB that the system keeps per
+// resident CTA), so that a CTA of the next launch fits beside one of this launch.
+constexpr int kBgmvSmemCoResident = (228 * 1024 - 2 * 1024) / 2;
 
 inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 inline int floor_pow2(int v) { int r = 1; while (r * 2 <= v) r *= 2; return r; }
@@ -644,21 +664,31 @@ inline bool bgmv_plan(const BgmvProblem& b, BgmvParams* pp, const char** why) {
   }
   const int stageB = p.ER * b.r_max * 2;
   p.stage_bytes = round_up_i(std::max(stageA, stageB), 128);
-  p.red_pitch = Rc + 2;
+  // floats per token row: a multiple of 4 (16-byte reads) that is 8 modulo 16, so that the eight token
+  // rows of a half warp start in different banks
+  p.red_pitch = (Rc % 16 == 8) ? Rc : Rc + 8;
   const int red_bytes = round_up_i(kBgmvWarps * kBgmvTok * p.red_pitch * 4, 128);
   p.pitchT = round_up_i(Q * 2, 128) + 64;
   p.tmp_bytes = round_up_i(kBgmvTok * p.pitchT, 128);
   const int bar_bytes = 256;
-  const int fixed = red_bytes + 2 * p.tmp_bytes + bar_bytes;
-  const int ring_kb = bgmv_options().ring_kb > 0 ? bgmv_options().ring_kb : kBgmvDefaultRingKb;
-  int NS = std::min(std::max(tiles, 2), (kBgmvSmemMax - fixed) / p.stage_bytes);
+  int exp_tiles = 0;
+  for (int s = 0; s < st.n; ++s) exp_tiles += ceil_div_i(p.oc[s], p.ER);
+  if (exp_tiles > kBgmvMaxExpandTiles) { *why = "too many expand tiles per CTA"; return false; }
+  const int tab_bytes = round_up_i(std::max(exp_tiles, 1) * 8, 128);
+  const int fixed = red_bytes + 2 * p.tmp_bytes + tab_bytes + bar_bytes;
+  // ring: what fits beside a second CTA on the SM, unless the caller set a size (up to the whole SM)
+  const int ring_bytes = bgmv_options().ring_kb > 0 ? bgmv_options().ring_kb * 1024
+                                                    : std::max(kBgmvSmemCoResident - fixed - 256, 2 * p.stage_bytes);
+  int NS = std::min(std::max(tiles, 2), (kBgmvSmemMax - fixed - 256) / p.stage_bytes);
   NS = std::min(NS, kBgmvMaxStages);
-  NS = std::min(NS, std::max(2, ring_kb * 1024 / p.stage_bytes));
+  NS = std::min(NS, std::max(2, ring_bytes / p.stage_bytes));
   if (NS < 2) { *why = "shared memory too small for two stages"; return false; }
   p.NS = NS;
   p.off_red = NS * p.stage_bytes;
   p.off_tmp = p.off_red + red_bytes;
-  p.off_bar = p.off_tmp + 2 * p.tmp_bytes;
+  p.off_tab = p.off_tmp + 2 * p.tmp_bytes;
+  p.off_bar = p.off_tab + tab_bytes;
+  p.full_k = (p.KP == kBgmvKP && b.in_dim % kBgmvKP == 0) ? 1 : 0;
   p.use_pdl = bgmv_options().pdl ? 1 : 0;
   p.mode = b.mode;
   p.tmp_io = b.tmp_io;
@@ -680,10 +710,12 @@ inline int bgmv_launch(const BgmvProblem& b, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_device != dev) {
-    cudaError_t e = cudaFuncSetAttribute(bgmv_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBgmvSmemMax);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(bgmv_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBgmvSmemMax);
-    if (e != cudaSuccess) return fail(B200_LORA_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    const void* kernels[4] = {(const void*)bgmv_fused_kernel<false, false>, (const void*)bgmv_fused_kernel<false, true>,
+                              (const void*)bgmv_fused_kernel<true, false>, (const void*)bgmv_fused_kernel<true, true>};
+    for (const void* k : kernels) {
+      cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kBgmvSmemMax);
+      if (e != cudaSuccess) return fail(B200_LORA_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    }
     configured_device = dev;
   }
   cudaLaunchConfig_t cfg = {};
@@ -705,8 +737,11 @@ inline int bgmv_launch(const BgmvProblem& b, cudaStream_t stream) {
   }
   cfg.attrs = attrs;
   cfg.numAttrs = (unsigned)na;
-  cudaError_t e = p.mode == 3 ? cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<true>, p)
-                              : cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<false>, p);
+  cudaError_t e;
+  if (p.mode == 3)
+    e = p.full_k ? cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<true, true>, p) : cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<true, false>, p);
+  else
+    e = p.full_k ? cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<false, true>, p) : cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<false, false>, p);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return fail(B200_LORA_ECUDA, "bgmv_fused_kernel launch: %s", cudaGetErrorString(e));

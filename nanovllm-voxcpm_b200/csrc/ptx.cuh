@@ -103,6 +103,12 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uin
       : "memory");
 }
 
+// L2 prefetch of a contiguous global range by the TMA unit (no shared memory, no completion
+// to wait for); address and size multiples of 16 bytes.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
 // ------------------------------------------------------------------ cluster
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -116,6 +122,13 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t local_addr, uint32_t ct
 }
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// 8-byte store into the shared memory of a CTA of the cluster that also counts its bytes on
+// an mbarrier of that CTA (both addresses from mapa_shared): data and signal in one operation.
+__device__ __forceinline__ void st_async_b32x2(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b32 [%0], {%1, %2}, [%3];" ::"r"(cluster_addr),
+               "r"(a), "r"(b), "r"(cluster_bar)
+               : "memory");
 }
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release;" ::: "memory");
@@ -157,6 +170,11 @@ __device__ __forceinline__ uint4 ldg128(const void* gptr) {
 }
 __device__ __forceinline__ void stg128(void* gptr, uint4 v) {
   asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(gptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// y[0..8) += d[0..8) (bf16, one 16-byte reduction performed at the L2; nothing comes back)
+__device__ __forceinline__ void red_add_bf16x8(void* gptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(gptr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 // ------------------------------------------------- warp MMA, bf16 -> fp32
