@@ -87,7 +87,7 @@ def apply_options(args):
     from nanovllm_voxcpm_b200 import _native as N
 
     keys = {"cluster": N.OPT_CLUSTER, "pdl": N.OPT_PDL, "ring_kb": N.OPT_RING_KB,
-            "decode_kernel": N.OPT_DECODE_KERNEL, "smem_kb": N.OPT_SMEM_KB}
+            "decode_kernel": N.OPT_DECODE_KERNEL, "smem_kb": N.OPT_SMEM_KB, "ksplit": N.OPT_KSPLIT}
     for item in args.option:
         key, _, value = item.partition("=")
         N.set_option(keys[key], int(value))

@@ -342,6 +342,7 @@ int lora_b200_shrink_allreduce_expand(void* y, int64_t y_ld, const void* x, int6
 #define B200_LORA_OPT_PDL 2     /* 1 = launch with programmatic stream serialization (default), 0 = off */
 #define B200_LORA_OPT_RING_KB 3 /* cap of the shared-memory stage ring in KB, 0 = as large as fits */
 #define B200_LORA_OPT_DECODE_KERNEL 4 /* fused decode kernel: 0 = row-split, else column-split where only that takes the shape (default); 1 = row-split only; 2 = column-split only */
+#define B200_LORA_OPT_KSPLIT 6 /* fused decode kernel: 1 = deal the K parts of long input rows (>= 1024 columns per CTA of a cluster) over the cluster (default), 0 = always split the rank rows */
 #define B200_LORA_OPT_SMEM_KB 5 /* column-split kernel: cap of shared memory per CTA in KB, 0 = 112 (two CTAs per SM) */
 
 /* Sets a tuning knob; returns 0, or B200_LORA_EINVAL for an unknown key / value.

@@ -98,7 +98,7 @@ _SIGNATURES = {
     "lora_b200_device_status": (c_int32, [POINTER(c_int32), c_int32]),
 }
 
-OPT_CLUSTER, OPT_PDL, OPT_RING_KB, OPT_DECODE_KERNEL, OPT_SMEM_KB = 1, 2, 3, 4, 5
+OPT_CLUSTER, OPT_PDL, OPT_RING_KB, OPT_DECODE_KERNEL, OPT_SMEM_KB, OPT_KSPLIT = 1, 2, 3, 4, 5, 6
 DECODE_AUTO, DECODE_ROW_SPLIT, DECODE_COLUMN_SPLIT = 0, 1, 2
 META_GRAPH, META_KERNEL, META_EAGER = 0, 1, 2
 

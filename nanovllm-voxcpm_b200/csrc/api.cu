@@ -124,6 +124,10 @@ int lora_b200_set_option(int32_t key, int32_t value) {
     g_decode_kernel = value;
     return B200_LORA_OK;
   }
+  if (key == B200_LORA_OPT_KSPLIT) {
+    bgmv_options().ksplit = value != 0;
+    return B200_LORA_OK;
+  }
   if (key == B200_LORA_OPT_SMEM_KB) {
     if (value < 0 || value > 227) return fail(B200_LORA_EINVAL, "shared-memory cap %d KB outside [0, 227]", value);
     bgmv_split_options().smem_kb = value;

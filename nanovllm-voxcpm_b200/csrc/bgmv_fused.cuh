@@ -32,6 +32,8 @@
 // Rows whose slot is -1 are in no bucket and are never read or written.
 #pragma once
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -99,6 +101,8 @@ struct BgmvParams {
   int tmp_bytes;    // bytes of one tmp buffer
   int off_red, off_tmp, off_tab, off_bar;
   int full_k;       // every K part has all 1024 columns
+  int ksplit;       // 1: the K parts (not the rank rows) are dealt over the CTAs of a cluster
+  int pitchR, recv_bytes, off_recv;  // K split: floats per token row / bytes of one buffer of received partial sums
   int use_pdl;
   int mode;         // 0 fused, 1 shrink only (tmp_io written), 2 expand only (tmp_io read), 3 overwrite y
   float* tmp_io;
@@ -132,9 +136,9 @@ __device__ __forceinline__ void bgmv_fill_rows_without_delta(const BgmvParams& p
 #ifndef BGMV_MINBLOCKS
 #define BGMV_MINBLOCKS 2
 #endif
-// kOverwrite = mode 3, compiled separately so that the add path carries none of its branches;
+// kMode = BgmvParams::mode, compiled separately so that no path carries the branches of another;
 // kFullK = every K part has all 1024 columns (in_dim a multiple of 1024): no column checks in the shrink
-template <bool kOverwrite, bool kFullK>
+template <int kMode, bool kFullK>
 __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kernel(const __grid_constant__ BgmvParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -142,6 +146,8 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
   const int C = 1 << p.c_shift;
   const int c = (int)cluster_ctarank();
   const int NS = p.NS;
+  constexpr bool kOverwrite = kMode == 3;
+  constexpr int mode = kMode;
 
   B200_TRACE_POINT(0)
   // Let the next launch of the stream start at once: before its own griddepcontrol.wait it only
@@ -192,13 +198,18 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
   const int n = p.st.n;
   const int in_dim = p.in_dim;
   const int Q = n * r_eff;                                       // stacked rank rows
-  const int Rc = ((((Q + C - 1) >> p.c_shift) + 7) & ~7);        // rows owned per CTA
-  const int q_lo = min(c * Rc, Q);
-  const int mode = p.mode;
+  // Shrink work of the cluster: either the rank rows are split over the CTAs (each takes all K parts of
+  // its rows, the bf16 results are all-gathered), or - long input rows - the K parts are dealt over the
+  // CTAs (each takes all rank rows of its K parts, the fp32 partial sums are exchanged and added).
+  const bool ksplit = (kMode == 0 || kMode == 3) && p.ksplit != 0;
+  const int Rc = ksplit ? Q : ((((Q + C - 1) >> p.c_shift) + 7) & ~7);  // rows owned per CTA
+  const int q_lo = ksplit ? 0 : min(c * Rc, Q);
   const int rows_c = mode == 2 ? 0 : min(q_lo + Rc, Q) - q_lo;   // multiple of 8, may be 0 (expand only: no shrink rows)
   const int nt_c = rows_c >> 3;                                  // 8-row tiles of this CTA
   const int KP = p.KP, pitchA = p.pitchA, ER = p.ER, nkp = p.nkp;
-  const int shrink_tiles = nt_c * nkp;
+  const int kp0 = ksplit ? c : 0, kstep = ksplit ? C : 1;        // K parts of this CTA: kp0, kp0 + kstep, ...
+  const int nkp_c = ksplit ? (nkp > c ? (nkp - c + C - 1) >> p.c_shift : 0) : nkp;
+  const int shrink_tiles = nt_c * nkp_c;
   int e_lo[B200_LORA_MAX_SLICES], e_n[B200_LORA_MAX_SLICES], e_tiles[B200_LORA_MAX_SLICES];
   int tiles_exp = 0;
 #pragma unroll
@@ -214,8 +225,9 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
   }
   const int npass = (cnt + kBgmvTok - 1) >> 4;
   const int total = (shrink_tiles + tiles_exp) * npass;
-  // bytes a pass delivers into this CTA's tmp buffer: 16 token rows of all Q stacked rank rows
-  const uint32_t gather_bytes = (uint32_t)(kBgmvTok * Q * 2);
+  // bytes a pass delivers into this CTA: 16 token rows of all Q stacked rank rows, as bf16 once
+  // (all-gather) or as fp32 from every CTA of the cluster (K split)
+  const uint32_t gather_bytes = ksplit ? (uint32_t)(C * kBgmvTok * Q * 4) : (uint32_t)(kBgmvTok * Q * 2);
   if (tid == 0 && (mode == 0 || mode == 3)) {
     mbar_arrive_expect_tx(tmp_ready_bars, gather_bytes);                      // pass 0
     if (npass > 1) mbar_arrive_expect_tx(tmp_ready_bars + 8u, gather_bytes);  // pass 1
@@ -236,12 +248,13 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
     const int q0_s = i_qs, q0_r = i_qr;
     int p_stage = 0, p_round = 0;
     const int npro = min(NS, total);
+#pragma unroll 1
     for (int it = 0; it < total; ++it) {
       if (p_round > 0) mbar_wait_bounded(empty_bar(p_stage), (uint32_t)((p_round & 1) ^ 1), abort_flag);
       const uint32_t sbase = ring_base + (uint32_t)p_stage * (uint32_t)p.stage_bytes;
       const uint32_t fb = full_bar(p_stage);
       if (i_shrink) {
-        const int k0 = i_kp * KP;
+        const int k0 = (kp0 + i_kp * kstep) * KP;
         const uint32_t row_bytes = (uint32_t)min(KP, in_dim - k0) * 2u;
         const void* aptr = nullptr;
 #pragma unroll
@@ -267,7 +280,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
         if (i_j == nt_c) {
           i_j = 0; i_qs = q0_s; i_qr = q0_r;
           // (shrink-only launches have no expand tiles: the next pass starts with shrink tiles again)
-          if (++i_kp == nkp) { i_kp = 0; i_shrink = tiles_exp > 0 ? 0 : 1; i_s = 0; i_et = 0; }
+          if (++i_kp == nkp_c) { i_kp = 0; i_shrink = tiles_exp > 0 ? 0 : 1; i_s = 0; i_et = 0; }
         }
       } else {
 #pragma unroll
@@ -303,9 +316,24 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
         B200_TRACE_PRODUCER(3)
         // The ring is full and the previous launch of the stream may still be running: ask the L2 for
         // the rest of this CTA's weights now, so that the refills that follow the wait find them there.
+        if (shrink_tiles + tiles_exp > npro && ksplit) {
+          // one row piece per lane: rank row q of this CTA's K part ikp
+#pragma unroll 1
+          for (int idx = lane; idx < rows_c * nkp_c; idx += 32) {
+            const int ikp = idx / max(rows_c, 1), q = idx - ikp * rows_c;
+            const int s = q / r_eff, r0 = q - s * r_eff, k0 = (kp0 + ikp * kstep) * KP;
+            const void* aptr = nullptr;
+#pragma unroll
+            for (int ss = 0; ss < B200_LORA_MAX_SLICES; ++ss)
+              if (ss == s) aptr = p.st.a[ss];
+            bulk_prefetch_l2(static_cast<const __nv_bfloat16*>(aptr) + ((int64_t)slot * p.r_max + r0) * in_dim + k0,
+                             (uint32_t)min(KP, in_dim - k0) * 2u);
+          }
+        }
         if (shrink_tiles + tiles_exp > npro && lane == 0) {
           int q = q_lo;
-          const int q_hi = q_lo + rows_c;
+          const int q_hi = ksplit ? q_lo : q_lo + rows_c;
+#pragma unroll 1
           while (q < q_hi) {
             const int s = q / r_eff, r0 = q - s * r_eff;
             const int nr = min(r_eff - r0, q_hi - q);
@@ -342,6 +370,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
 
   // expand tile e of this CTA (ring order): x = first y column, y = rows | slice << 16
   int2* etab = reinterpret_cast<int2*>(smem + p.off_tab);
+#pragma unroll 1
   for (int e = tid; e < tiles_exp; e += kBgmvConsumers) {
     int s_e = 0, et = e;
 #pragma unroll
@@ -360,13 +389,21 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
   const int x_col = warp * 32 + t * 8;  // shrink: first column of the thread inside a K part (block i adds 256)
   const int y_col = rb + 8 * t;         // expand: first of the thread's 8 output columns inside a tile
   if (p.use_pdl) {
-    if (rows_c > 0) {
-      for (int kc = x_col; kc < in_dim; kc += kBgmvWarps * 32) {
+#pragma unroll 1
+    for (int ikp = 0; ikp < (rows_c > 0 ? nkp_c : 0); ++ikp) {
+      const int k0 = (kp0 + ikp * kstep) * KP;
+#pragma unroll 1
+      for (int kc = k0 + x_col; kc < min(k0 + KP, in_dim); kc += kBgmvWarps * 32) {
         if (tok0_lo >= 0) prefetch_l2(p.x + (int64_t)tok0_lo * p.x_ld + kc);
         if (tok0_hi >= 0) prefetch_l2(p.x + (int64_t)tok0_hi * p.x_ld + kc);
       }
     }
+#ifdef ABL_NOYPF
+    if (false) {
+#else
     if (!kOverwrite) {  // the lines of y that this thread's reductions will land in
+#endif
+#pragma unroll 1
       for (int e = 0; e < tiles_exp; ++e) {
         const int2 te = etab[e];
         if (y_col < (te.y & 0xffff)) {
@@ -394,6 +431,8 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
   const float* const red_rd = red + (size_t)it_tok * p.red_pitch + (it_q - q_lo);
   const uint32_t it_off = (uint32_t)(it_tok * p.pitchT + it_q * 2);
   const uint32_t tmp_u32 = smem_u32(tmp_base);
+  const uint32_t recv_u32 = smem_u32(smem + p.off_recv);
+  const uint32_t it_roff = (uint32_t)(it_tok * p.pitchR + it_q) * 4u;  // K split: the item inside one sender's block
 
   if (p.use_pdl) griddep_wait();  // x and y of this launch are final from here on
   if (kOverwrite) bgmv_fill_rows_without_delta(p, bucket * C + c, (int)gridDim.y * C, tid, kBgmvConsumers);
@@ -406,6 +445,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
     if (++c_stage == NS) { c_stage = 0; c_parity ^= 1u; stage_addr = ring_base; }
   };
 
+#pragma unroll 1
   for (int pass = 0; pass < npass; ++pass) {
     int tok_lo = tok0_lo, tok_hi = tok0_hi;
     if (pass > 0) {
@@ -421,8 +461,9 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
     __nv_bfloat16* const yhi_p = p.y + (int64_t)max(tok_hi, 0) * p.y_ld + y_col;
 
     // ===== shrink: red[warp][tok][row] = x[16 tok, K blocks of this warp] . A_rows^T =====
-    for (int kp = 0; kp < (rows_c > 0 ? nkp : 0); ++kp) {
-      const int k0 = kp * KP;
+#pragma unroll 1
+    for (int kp = 0; kp < (rows_c > 0 ? nkp_c : 0); ++kp) {
+      const int k0 = (kp0 + kp * kstep) * KP;
       // activation fragments of this warp's 32-column blocks, kept for all row tiles
       uint4 xlo[kBgmvXBlocks], xhi[kBgmvXBlocks];
 #pragma unroll
@@ -433,36 +474,71 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
           if (tok_hi >= 0) xhi[i] = ldg128_nc(xhi_p + k0 + 256 * i);
         }
       }
-      for (int j = 0; j < nt_c; ++j) {
+      // kTiles (1 or 2) 8-row tiles of the ring against the warp's activation fragments: all loads
+      // first, then the independent MMA chains of both tiles, then the stores; sums of the K blocks go
+      // to the warp's rows of the reduction buffer (added to what earlier K parts left there)
+      auto shrink_tiles_fn = [&](auto n_tiles, int j, uint32_t addr0, uint32_t addr1) {
+        constexpr int kTiles = decltype(n_tiles)::value;
+        float acc[kTiles][2][4];
+#pragma unroll
+        for (int u = 0; u < kTiles; ++u)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) acc[u][h][0] = acc[u][h][1] = acc[u][h][2] = acc[u][h][3] = 0.f;
+#pragma unroll
+        for (int i = 0; i < kBgmvXBlocks; ++i) {
+          uint4 w[kTiles];
+#pragma unroll
+          for (int u = 0; u < kTiles; ++u) {
+            w[u] = make_uint4(0, 0, 0, 0);
+            if (kFullK || (x_col + 256 * i < KP && k0 + x_col + 256 * i < in_dim))
+              w[u] = lds128((u == 0 ? addr0 : addr1) + a_off + 512u * i);
+          }
+#pragma unroll
+          for (int u = 0; u < kTiles; ++u) {
+            mma_bf16_16816(acc[u][0], xlo[i].x, xhi[i].x, xlo[i].y, xhi[i].y, w[u].x, w[u].y);
+            mma_bf16_16816(acc[u][1], xlo[i].z, xhi[i].z, xlo[i].w, xhi[i].w, w[u].z, w[u].w);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kTiles; ++u) {
+          // acc holds (tok g | g+8, rank rows 8(j+u)+2t, 8(j+u)+2t+1)
+          float2* r0 = reinterpret_cast<float2*>(red_wr + 8 * (j + u));
+          float2* r1 = reinterpret_cast<float2*>(red_wr + 8 * p.red_pitch + 8 * (j + u));
+          float2 a = make_float2(0.f, 0.f), b = a;
+          if (kp != 0) { a = *r0; b = *r1; }
+          *r0 = make_float2(a.x + acc[u][0][0] + acc[u][1][0], a.y + acc[u][0][1] + acc[u][1][1]);
+          *r1 = make_float2(b.x + acc[u][0][2] + acc[u][1][2], b.y + acc[u][0][3] + acc[u][1][3]);
+        }
+      };
+      int j = 0;
+#ifndef BGMV_SHRINK_SINGLE
+#pragma unroll 1
+      for (; j + 1 < nt_c; j += 2) {
+        const int s0 = c_stage;
+        const uint32_t a0 = stage_addr;
+        mbar_wait_bounded(full_bar(s0), c_parity, abort_flag);
+        if (kp == 0 && j == 0 && pass == 0) { B200_TRACE_POINT(5) }
+        advance();
+        const int s1 = c_stage;
+        const uint32_t a1 = stage_addr;
+        mbar_wait_bounded(full_bar(s1), c_parity, abort_flag);
+        advance();
+        shrink_tiles_fn(std::integral_constant<int, 2>{}, j, a0, a1);
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(empty_bar(s0));
+          mbar_arrive(empty_bar(s1));
+        }
+      }
+#endif
+#pragma unroll 1
+      for (; j < nt_c; ++j) {
         mbar_wait_bounded(full_bar(c_stage), c_parity, abort_flag);
         if (kp == 0 && j == 0 && pass == 0) { B200_TRACE_POINT(5) }
-        // two independent accumulator chains halve the dependent-MMA latency
-        float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
-        uint4 w[kBgmvXBlocks];
-#pragma unroll
-        for (int i = 0; i < kBgmvXBlocks; ++i) {
-          w[i] = make_uint4(0, 0, 0, 0);
-          if (kFullK || (x_col + 256 * i < KP && k0 + x_col + 256 * i < in_dim)) w[i] = lds128(stage_addr + a_off + 512u * i);
-        }
-#pragma unroll
-        for (int i = 0; i < kBgmvXBlocks; ++i) {
-          mma_bf16_16816(acc, xlo[i].x, xhi[i].x, xlo[i].y, xhi[i].y, w[i].x, w[i].y);
-          mma_bf16_16816(acc2, xlo[i].z, xhi[i].z, xlo[i].w, xhi[i].w, w[i].z, w[i].w);
-        }
+        shrink_tiles_fn(std::integral_constant<int, 1>{}, j, stage_addr, stage_addr);
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(c_stage));
         advance();
-        // acc holds (tok g | g+8, rank rows 8j+2t, 8j+2t+1): accumulate over K parts per warp
-        float2* r0 = reinterpret_cast<float2*>(red_wr + 8 * j);
-        float2* r1 = reinterpret_cast<float2*>(red_wr + 8 * p.red_pitch + 8 * j);
-        if (kp == 0) {
-          *r0 = make_float2(acc[0] + acc2[0], acc[1] + acc2[1]);
-          *r1 = make_float2(acc[2] + acc2[2], acc[3] + acc2[3]);
-        } else {
-          const float2 a = *r0, b = *r1;
-          *r0 = make_float2(a.x + acc[0] + acc2[0], a.y + acc[1] + acc2[1]);
-          *r1 = make_float2(b.x + acc[2] + acc2[2], b.y + acc[3] + acc2[3]);
-        }
       }
     }
     if (pass == 0) { B200_TRACE_POINT(6) }
@@ -487,6 +563,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
       int trow = -1;
       if (pass * kBgmvTok + tok < cnt) trow = p.sorted_idx[start + pass * kBgmvTok + tok];
       if (trow >= p.T) trow = -1;
+#pragma unroll 1
       for (int pr = tid & 15; pr < (Q >> 1); pr += 16) {
         const int q = 2 * pr, s = q / r_eff, rr = q - s * r_eff;
         float2 v = make_float2(0.f, 0.f);
@@ -512,10 +589,18 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
             dst[0] = make_float2(a.x * sc, a.y * sc);
             dst[1] = make_float2(a.z * sc, a.w * sc);
           }
+        } else if (ksplit) {
+          // to every CTA of the cluster (this one included): this CTA's fp32 partial sums over its K parts,
+          // into the block the receiver keeps for this sender
+          const uint32_t dst = recv_u32 + (uint32_t)(((pass & 1) * C + c) * (kBgmvTok * p.pitchR * 4)) + it_roff;
+#pragma unroll 1
+          for (int rc = 0; rc < C; ++rc)
+            st_async_f32x4(mapa_shared(dst, (uint32_t)rc), a, mapa_shared(tmp_ready_bar, (uint32_t)rc));
         } else {
           // to every CTA of the cluster (this one included): 8 bytes of tmp + their count on the
           // receiver's barrier in one operation
           const uint32_t v0 = pack_bf16x2(a.x * sc, a.y * sc), v1 = pack_bf16x2(a.z * sc, a.w * sc);
+#pragma unroll 1
           for (int rc = 0; rc < C; ++rc)
             st_async_b32x2(mapa_shared(tmp_cur + it_off, (uint32_t)rc), v0, v1, mapa_shared(tmp_ready_bar, (uint32_t)rc));
         }
@@ -528,59 +613,89 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
       // (the wait also orders the reduction buffer: no warp passes it before every warp of every CTA
       // of the cluster has summed and sent its items, so the next pass may refill the buffer)
       mbar_wait_bounded_acquire_cluster(tmp_ready_bar, (uint32_t)((pass >> 1) & 1), abort_flag);
+      if (ksplit) {
+        // add the C partial sums of this thread's item, scale, round: tmp of this pass, kept locally
+        if (has_item) {
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+          const float* src = reinterpret_cast<const float*>(smem + p.off_recv) + (size_t)(pass & 1) * C * kBgmvTok * p.pitchR +
+                             (size_t)it_tok * p.pitchR + it_q;
+#pragma unroll 1
+          for (int rc = 0; rc < C; ++rc) {
+            const float4 v = *reinterpret_cast<const float4*>(src + (size_t)rc * kBgmvTok * p.pitchR);
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+          }
+          *reinterpret_cast<uint2*>(tmp_base + (size_t)(pass & 1) * p.tmp_bytes + it_off) =
+              make_uint2(pack_bf16x2(a.x * sc, a.y * sc), pack_bf16x2(a.z * sc, a.w * sc));
+        }
+        named_bar_sync(1, kBgmvConsumers);
+      }
       if (pass == 0) { B200_TRACE_POINT(9) }
     }
 
     // ===== expand: y[tok, cols] += tmp[16 tok, r] . B_rows^T ======================
-    for (int e = 0; e < tiles_exp; ++e) {
-      const int2 te = etab[e];
-      const int nrows = te.y & 0xffff;
-      const uint32_t a_addr = tmp_cur + t_off + (uint32_t)((te.y >> 16) * r_eff * 2);
-      mbar_wait_bounded(full_bar(c_stage), c_parity, abort_flag);
-      if (pass == 0 && e < 5) { B200_TRACE_POINT(12 + 4 * e) }
-      if (rb < nrows) {  // ER <= 256: one 32-row block per warp and tile
-        float d[4][4];
+    // one tile of the ring per step: one 32-row block per warp (ER <= 256). Rows of a stage beyond the
+    // tile's rows hold stale bytes; their products land in columns that are not written.
+    auto expand_fn = [&](int e, uint32_t addr0) {
+      constexpr int kTiles = 1;
+      const uint32_t addr1 = addr0;
+      int2 te[kTiles];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.f;
-        for (int kb = 0; kb < kblocks; ++kb) {
-          const uint4 alo = lds128(a_addr + 64u * kb);
-          const uint4 ahi = lds128(a_addr + 8u * (uint32_t)p.pitchT + 64u * kb);
+      for (int u = 0; u < kTiles; ++u) te[u] = etab[e + u];
+      float d[kTiles][4][4];
+#pragma unroll
+      for (int u = 0; u < kTiles; ++u)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) d[u][j][0] = d[u][j][1] = d[u][j][2] = d[u][j][3] = 0.f;
+#pragma unroll 1
+      for (int kb = 0; kb < kblocks; ++kb) {
+#pragma unroll
+        for (int u = 0; u < kTiles; ++u) {
+          const uint32_t a_addr = tmp_cur + t_off + (uint32_t)((te[u].y >> 16) * r_eff * 2) + 64u * kb;
+          const uint32_t w_addr = (u == 0 ? addr0 : addr1) + w_off + 64u * kb;
+          const uint4 alo = lds128(a_addr);
+          const uint4 ahi = lds128(a_addr + 8u * (uint32_t)p.pitchT);
           uint4 w[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) w[j] = lds128(stage_addr + w_off + 2u * j * pitchB + 64u * kb);
+          for (int j = 0; j < 4; ++j) w[j] = lds128(w_addr + 2u * j * pitchB);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) mma_bf16_16816(d[j], alo.x, ahi.x, alo.y, ahi.y, w[j].x, w[j].y);
+          for (int j = 0; j < 4; ++j) mma_bf16_16816(d[u][j], alo.x, ahi.x, alo.y, ahi.y, w[j].x, w[j].y);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) mma_bf16_16816(d[j], alo.z, ahi.z, alo.w, ahi.w, w[j].z, w[j].w);
+          for (int j = 0; j < 4; ++j) mma_bf16_16816(d[u][j], alo.z, ahi.z, alo.w, ahi.w, w[j].z, w[j].w);
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar(c_stage));  // the stage is in registers now
-        if (pass == 0 && e < 5) { B200_TRACE_POINT(13 + 4 * e) }
-        if (y_col < nrows) {
+      }
+#pragma unroll
+      for (int u = 0; u < kTiles; ++u) {
+        if (y_col < (te[u].y & 0xffff)) {
           if (kOverwrite) {
             if (tok_lo >= 0)
-              stg128(ylo_p + te.x, make_uint4(pack_bf16x2(d[0][0], d[0][1]), pack_bf16x2(d[1][0], d[1][1]),
-                                              pack_bf16x2(d[2][0], d[2][1]), pack_bf16x2(d[3][0], d[3][1])));
+              stg128(ylo_p + te[u].x, make_uint4(pack_bf16x2(d[u][0][0], d[u][0][1]), pack_bf16x2(d[u][1][0], d[u][1][1]),
+                                                 pack_bf16x2(d[u][2][0], d[u][2][1]), pack_bf16x2(d[u][3][0], d[u][3][1])));
             if (tok_hi >= 0)
-              stg128(yhi_p + te.x, make_uint4(pack_bf16x2(d[0][2], d[0][3]), pack_bf16x2(d[1][2], d[1][3]),
-                                              pack_bf16x2(d[2][2], d[2][3]), pack_bf16x2(d[3][2], d[3][3])));
+              stg128(yhi_p + te[u].x, make_uint4(pack_bf16x2(d[u][0][2], d[u][0][3]), pack_bf16x2(d[u][1][2], d[u][1][3]),
+                                                 pack_bf16x2(d[u][2][2], d[u][2][3]), pack_bf16x2(d[u][3][2], d[u][3][3])));
           } else {
             // The delta is rounded to bf16 and added to y by one 16-byte reduction at the L2: y never
             // travels to the SM and nothing waits for it. Each element of y receives exactly one
             // reduction per launch, so the result does not depend on their order.
             if (tok_lo >= 0)
-              red_add_bf16x8(ylo_p + te.x, pack_bf16x2(d[0][0], d[0][1]), pack_bf16x2(d[1][0], d[1][1]),
-                             pack_bf16x2(d[2][0], d[2][1]), pack_bf16x2(d[3][0], d[3][1]));
+              red_add_bf16x8(ylo_p + te[u].x, pack_bf16x2(d[u][0][0], d[u][0][1]), pack_bf16x2(d[u][1][0], d[u][1][1]),
+                             pack_bf16x2(d[u][2][0], d[u][2][1]), pack_bf16x2(d[u][3][0], d[u][3][1]));
             if (tok_hi >= 0)
-              red_add_bf16x8(yhi_p + te.x, pack_bf16x2(d[0][2], d[0][3]), pack_bf16x2(d[1][2], d[1][3]),
-                             pack_bf16x2(d[2][2], d[2][3]), pack_bf16x2(d[3][2], d[3][3]));
+              red_add_bf16x8(yhi_p + te[u].x, pack_bf16x2(d[u][0][2], d[u][0][3]), pack_bf16x2(d[u][1][2], d[u][1][3]),
+                             pack_bf16x2(d[u][2][2], d[u][2][3]), pack_bf16x2(d[u][3][2], d[u][3][3]));
           }
         }
-      } else {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar(c_stage));
       }
-      if (pass == 0 && e < 5) { B200_TRACE_POINT(14 + 4 * e) }
+    };
+    int e = 0;
+#pragma unroll 1
+    for (; e < tiles_exp; ++e) {
+      mbar_wait_bounded(full_bar(c_stage), c_parity, abort_flag);
+      if (pass == 0 && e < 10) { B200_TRACE_POINT(12 + 2 * e) }
+      expand_fn(e, stage_addr);
+      if (pass == 0 && e < 10) { B200_TRACE_POINT(13 + 2 * e) }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(c_stage));
       advance();
     }
     if (pass == 0) { B200_TRACE_POINT(10) }
@@ -594,6 +709,7 @@ struct BgmvOptions {
   int cluster = 0;   // 0 = auto
   int pdl = 1;
   int ring_kb = 0;   // cap of the stage ring in KB (0 = default)
+  int ksplit = 1;    // 1 = deal K parts over the cluster when the input rows are long enough (default)
 };
 inline BgmvOptions& bgmv_options() {
   static BgmvOptions o;
@@ -638,8 +754,13 @@ inline bool bgmv_plan(const BgmvProblem& b, BgmvParams* pp, const char** why) {
     const int busy = std::min(b.n_buckets, std::max(b.T, 1));
     C = busy <= 37 ? 4 : (busy <= 74 ? 2 : 1);
   }
-  while (C < 8 && round_up_i(ceil_div_i(Q, C), 8) > kBgmvMaxRc) C *= 2;
-  const int Rc = round_up_i(ceil_div_i(Q, C), 8);
+  // K split: at least one K part (1024 columns) per CTA of the cluster and all rank rows in one CTA;
+  // the shrink-only / expand-only pair of the tensor-parallel exchange keeps the row split
+  const int nkp_all = ceil_div_i(b.in_dim, kBgmvKP);
+  const bool ksplit = bgmv_options().ksplit && C > 1 && (b.mode == 0 || b.mode == 3) && nkp_all >= C && Q <= kBgmvMaxRc;
+  if (!ksplit)
+    while (C < 8 && round_up_i(ceil_div_i(Q, C), 8) > kBgmvMaxRc) C *= 2;
+  const int Rc = ksplit ? Q : round_up_i(ceil_div_i(Q, C), 8);
   if (Rc > kBgmvMaxRc) { *why = "n_slices * r_max too large for one cluster"; return false; }
 
   BgmvParams p;
@@ -656,7 +777,7 @@ inline bool bgmv_plan(const BgmvProblem& b, BgmvParams* pp, const char** why) {
   const int stageA = 8 * p.pitchA;
   p.ER = std::max(32, std::min(256, floor_pow2(16384 / (b.r_max * 2))));
   p.er_shift = log2_exact(p.ER);
-  int tiles = (Rc / 8) * p.nkp;
+  int tiles = (Rc / 8) * (ksplit ? ceil_div_i(p.nkp, C) : p.nkp);
   for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) p.oc[s] = 0;
   for (int s = 0; s < st.n; ++s) {
     p.oc[s] = round_up_i(ceil_div_i(st.out[s], C), 32);
@@ -675,7 +796,10 @@ inline bool bgmv_plan(const BgmvProblem& b, BgmvParams* pp, const char** why) {
   for (int s = 0; s < st.n; ++s) exp_tiles += ceil_div_i(p.oc[s], p.ER);
   if (exp_tiles > kBgmvMaxExpandTiles) { *why = "too many expand tiles per CTA"; return false; }
   const int tab_bytes = round_up_i(std::max(exp_tiles, 1) * 8, 128);
-  const int fixed = red_bytes + 2 * p.tmp_bytes + tab_bytes + bar_bytes;
+  p.ksplit = ksplit ? 1 : 0;
+  p.pitchR = Q + 4;
+  p.recv_bytes = ksplit ? C * kBgmvTok * p.pitchR * 4 : 0;
+  const int fixed = red_bytes + 2 * p.tmp_bytes + 2 * p.recv_bytes + tab_bytes + bar_bytes;
   // ring: what fits beside a second CTA on the SM, unless the caller set a size (up to the whole SM)
   const int ring_bytes = bgmv_options().ring_kb > 0 ? bgmv_options().ring_kb * 1024
                                                     : std::max(kBgmvSmemCoResident - fixed - 256, 2 * p.stage_bytes);
@@ -686,7 +810,8 @@ inline bool bgmv_plan(const BgmvProblem& b, BgmvParams* pp, const char** why) {
   p.NS = NS;
   p.off_red = NS * p.stage_bytes;
   p.off_tmp = p.off_red + red_bytes;
-  p.off_tab = p.off_tmp + 2 * p.tmp_bytes;
+  p.off_recv = p.off_tmp + 2 * p.tmp_bytes;
+  p.off_tab = p.off_recv + 2 * p.recv_bytes;
   p.off_bar = p.off_tab + tab_bytes;
   p.full_k = (p.KP == kBgmvKP && b.in_dim % kBgmvKP == 0) ? 1 : 0;
   p.use_pdl = bgmv_options().pdl ? 1 : 0;
@@ -710,8 +835,10 @@ inline int bgmv_launch(const BgmvProblem& b, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_device != dev) {
-    const void* kernels[4] = {(const void*)bgmv_fused_kernel<false, false>, (const void*)bgmv_fused_kernel<false, true>,
-                              (const void*)bgmv_fused_kernel<true, false>, (const void*)bgmv_fused_kernel<true, true>};
+    const void* kernels[8] = {(const void*)bgmv_fused_kernel<0, false>, (const void*)bgmv_fused_kernel<0, true>,
+                              (const void*)bgmv_fused_kernel<1, false>, (const void*)bgmv_fused_kernel<1, true>,
+                              (const void*)bgmv_fused_kernel<2, false>, (const void*)bgmv_fused_kernel<2, true>,
+                              (const void*)bgmv_fused_kernel<3, false>, (const void*)bgmv_fused_kernel<3, true>};
     for (const void* k : kernels) {
       cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kBgmvSmemMax);
       if (e != cudaSuccess) return fail(B200_LORA_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -738,10 +865,15 @@ inline int bgmv_launch(const BgmvProblem& b, cudaStream_t stream) {
   cfg.attrs = attrs;
   cfg.numAttrs = (unsigned)na;
   cudaError_t e;
-  if (p.mode == 3)
-    e = p.full_k ? cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<true, true>, p) : cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<true, false>, p);
-  else
-    e = p.full_k ? cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<false, true>, p) : cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<false, false>, p);
+#define B200_BGMV_LAUNCH(M) \
+  (p.full_k ? cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<M, true>, p) : cudaLaunchKernelEx(&cfg, bgmv_fused_kernel<M, false>, p))
+  switch (p.mode) {
+    case 1: e = B200_BGMV_LAUNCH(1); break;
+    case 2: e = B200_BGMV_LAUNCH(2); break;
+    case 3: e = B200_BGMV_LAUNCH(3); break;
+    default: e = B200_BGMV_LAUNCH(0); break;
+  }
+#undef B200_BGMV_LAUNCH
   if (e != cudaSuccess) {
     cudaGetLastError();
     return fail(B200_LORA_ECUDA, "bgmv_fused_kernel launch: %s", cudaGetErrorString(e));

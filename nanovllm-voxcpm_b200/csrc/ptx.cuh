@@ -130,6 +130,11 @@ __device__ __forceinline__ void st_async_b32x2(uint32_t cluster_addr, uint32_t a
                "r"(a), "r"(b), "r"(cluster_bar)
                : "memory");
 }
+__device__ __forceinline__ void st_async_f32x4(uint32_t cluster_addr, float4 v, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(cluster_addr),
+               "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(cluster_bar)
+               : "memory");
+}
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release;" ::: "memory");
 }

@@ -164,6 +164,28 @@ def test_bgmv_many_tokens_per_slot_and_single_token():
     check_against_oracle(p1, out, y_in, what="one token")
 
 
+@pytest.mark.parametrize("ksplit", [1, 0])
+def test_bgmv_long_input_rows(ksplit):
+    """Input rows of 4 or more K parts of 1024 columns: the K parts are dealt over the cluster and fp32
+    partial sums are exchanged (or, switched off, every CTA walks all K parts of its rank rows)."""
+    N.set_option(N.OPT_KSPLIT, ksplit)
+    try:
+        # 3 slots x about 36 rows: three passes of 16 tokens (receive buffers alternate); 5 K parts on 4 CTAs
+        p = W.make_projection(15, 120, 4096, [1024], 3, 32, p_none=0.1)
+        out, y_in = run_add(p, N.IMPL_BGMV, "graph")
+        check_against_oracle(p, out, y_in, what=f"in 4096 / ksplit {ksplit}")
+        p = W.make_projection(16, 50, 5120, [512, 256], 5, 32, p_none=0.1)
+        out, y_in = run_add(p, N.IMPL_BGMV)
+        check_against_oracle(p, out, y_in, what=f"in 5120 / ksplit {ksplit}")
+        # ragged last K part (512 of 1024 columns), per-slot ranks and scales, overwrite form
+        sps = torch.tensor([1.0, 0.5, 2.0, 1.5])
+        p = W.make_projection(17, 40, 4608, [768], 4, 64, ranks=[64, 16, 32, 8])
+        out, y_in = run_add(p, N.IMPL_BGMV, use_ranks=True, scaling=0.5, scale_per_slot=sps, x_pad=8)
+        check_against_oracle(p, out, y_in, 0.5, sps, what=f"in 4608 / ksplit {ksplit}")
+    finally:
+        N.set_option(N.OPT_KSPLIT, 1)
+
+
 def test_bgmv_mixed_ranks_scales_and_strides():
     ranks = [(8, 16, 64)[s % 3] for s in range(6)]
     p = W.make_projection(9, 70, 2048, [2048, 256, 256], 6, 64, ranks=ranks, p_none=0.15)
