@@ -63,9 +63,6 @@ def parse_args():
     ap.add_argument("--glue", default="fused", choices=["fused", "torch"],
                     help="backbone workload: the steps between the projections as this library's single-launch kernels "
                          "(residual add + RMSNorm, RoPE + cache store, SiLU * up) or as plain torch ops")
-    ap.add_argument("--prefetch", default="off", choices=["on", "off"],
-                    help="backbone workload: request the next layer's adapter weights into L2 from a side stream during "
-                         "decode steps")
     ap.add_argument("--lora-order", default="first", choices=["first", "after"],
                     help="backbone workload, decode steps: multi-LoRA delta written before the base GEMM, which then "
                          "accumulates into it (first), or added after the GEMM as the reference does (after)")
@@ -78,7 +75,7 @@ def parse_args():
     ap.add_argument("--only", default=None, choices=["qkv", "o", "gate_up", "down"],
                     help="tuning: time one projection of every layer instead of all four")
     ap.add_argument("--option", action="append", default=[], metavar="KEY=VALUE",
-                    help="tuning: lora_b200_set_option before the run (cluster, pdl, ring_kb, decode_kernel, smem_kb)")
+                    help="tuning: lora_b200_set_option before the run (cluster, pdl, ring_kb, ksplit)")
     return ap.parse_args()
 
 
@@ -87,7 +84,7 @@ def apply_options(args):
     from nanovllm_voxcpm_b200 import _native as N
 
     keys = {"cluster": N.OPT_CLUSTER, "pdl": N.OPT_PDL, "ring_kb": N.OPT_RING_KB,
-            "decode_kernel": N.OPT_DECODE_KERNEL, "smem_kb": N.OPT_SMEM_KB, "ksplit": N.OPT_KSPLIT}
+            "ksplit": N.OPT_KSPLIT}
     for item in args.option:
         key, _, value = item.partition("=")
         N.set_option(keys[key], int(value))
@@ -730,7 +727,6 @@ def run_backbone_arm(args):
     model.init_random_(0)
     model.fill_adapter_slots_(cfg.max_loras, cfg.max_lora_rank, seed=1)
     model.fused_glue = args.glue == "fused" and args.impl == "b200"
-    model.prefetch_adapters = model.fused_glue and args.prefetch == "on"
     from nanovllm_voxcpm_b200 import layers as L_
 
     L_.LORA_FIRST = args.lora_order == "first" and args.impl == "b200"
@@ -773,7 +769,7 @@ def run_backbone_arm(args):
         "adapter_overhead": {"decode": base["decode_tokens_per_s"] / lora["decode_tokens_per_s"],
                              "prefill": base["prefill_tokens_per_s"] / lora["prefill_tokens_per_s"]},
         "device_status": N.device_status(), "impl": args.impl, "lora_backend": backend_name,
-        "glue": "fused kernels" if model.fused_glue else "torch ops", "adapter_prefetch": bool(model.prefetch_adapters),
+        "glue": "fused kernels" if model.fused_glue else "torch ops",
         "lora_order": "first" if L_.LORA_FIRST else "after",
     }))
 

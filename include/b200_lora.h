@@ -259,17 +259,6 @@ int lora_b200_glue_rope_kv_store(void* qkv, int64_t qkv_ld, int32_t T, int32_t n
 int lora_b200_glue_silu_mul(void* out, int64_t out_ld, const void* gate_up, int64_t gate_up_ld, int32_t T,
                             int32_t intermediate, int32_t dtype, void* stream);
 
-/*
- * L2 prefetch hint for the adapter weights of the buckets of a step: for every bucket g with slot_ids[g] in
- * [0, S) (and counts[g] > 0 when counts is given) and every slab j, asks for bytes_per_slot[j] bytes at
- * slabs[j] + slot * slot_stride_bytes[j]. At most 16 slabs per call, 16-byte aligned. Nothing is written and
- * nothing needs to be waited for; meant for a side stream, one layer ahead of the launches that read the slabs
- * (no counterpart in the reference, whose kernels fetch their weights on the critical path of the step).
- */
-int lora_b200_prefetch_slabs(const void* const* slabs, const int64_t* slot_stride_bytes, const int64_t* bytes_per_slot,
-                             int32_t n_slabs, const int32_t* slot_ids, const int32_t* counts, int32_t n_buckets, int32_t S,
-                             void* stream);
-
 /* conventions of lora_b200_build_metadata */
 #define B200_LORA_META_GRAPH 0  /* fixed buckets [-1, 0 .. S-1], bucket 0 always empty (CUDA-graph buffers) */
 #define B200_LORA_META_KERNEL 1 /* compact ids incl. the -1 bucket with its rows (LoRAKernelMeta.prepare_tensors) */
@@ -341,9 +330,7 @@ int lora_b200_shrink_allreduce_expand(void* y, int64_t y_ld, const void* x, int6
 #define B200_LORA_OPT_CLUSTER 1 /* CTAs per slot bucket: 1, 2, 4, 8; 0 = choose from n_buckets */
 #define B200_LORA_OPT_PDL 2     /* 1 = launch with programmatic stream serialization (default), 0 = off */
 #define B200_LORA_OPT_RING_KB 3 /* cap of the shared-memory stage ring in KB, 0 = as large as fits */
-#define B200_LORA_OPT_DECODE_KERNEL 4 /* fused decode kernel: 0 = row-split, else column-split where only that takes the shape (default); 1 = row-split only; 2 = column-split only */
 #define B200_LORA_OPT_KSPLIT 6 /* fused decode kernel: 1 = deal the K parts of long input rows (>= 1024 columns per CTA of a cluster) over the cluster (default), 0 = always split the rank rows */
-#define B200_LORA_OPT_SMEM_KB 5 /* column-split kernel: cap of shared memory per CTA in KB, 0 = 112 (two CTAs per SM) */
 
 /* Sets a tuning knob; returns 0, or B200_LORA_EINVAL for an unknown key / value.
  * No counterpart in the reference (its tile configs are static tables,

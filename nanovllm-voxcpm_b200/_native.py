@@ -81,9 +81,6 @@ _SIGNATURES = {
                   c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_void_p],
     ),
     "lora_b200_glue_silu_mul": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32, c_void_p]),
-    "lora_b200_prefetch_slabs": (
-        c_int32, [POINTER(c_void_p), POINTER(c_int64), POINTER(c_int64), c_int32, c_void_p, c_void_p, c_int32, c_int32, c_void_p],
-    ),
     "lora_b200_tp_allreduce": (
         c_int32, [c_void_p, c_void_p, c_int32, POINTER(c_void_p), c_int32, c_int32, c_int32, c_void_p],
     ),
@@ -98,8 +95,7 @@ _SIGNATURES = {
     "lora_b200_device_status": (c_int32, [POINTER(c_int32), c_int32]),
 }
 
-OPT_CLUSTER, OPT_PDL, OPT_RING_KB, OPT_DECODE_KERNEL, OPT_SMEM_KB, OPT_KSPLIT = 1, 2, 3, 4, 5, 6
-DECODE_AUTO, DECODE_ROW_SPLIT, DECODE_COLUMN_SPLIT = 0, 1, 2
+OPT_CLUSTER, OPT_PDL, OPT_RING_KB, OPT_KSPLIT = 1, 2, 3, 6
 META_GRAPH, META_KERNEL, META_EAGER = 0, 1, 2
 
 

@@ -166,41 +166,17 @@ class Decoder(nn.Module):
     #: residual add + RMSNorm, RoPE + cache store, SiLU * up; False: plain torch ops
     fused_glue = False
 
-    #: True: in decode-sized steps the adapter weights of layer i + 1 are requested into L2 from a side stream
-    #: while layer i runs (``lora.prefetch_slabs``), so that the multi-LoRA launches do not start with an HBM miss
-    prefetch_adapters = False
-    _side_stream = None
-
-    def _prefetch_next(self, i: int, rows: int) -> bool:
-        if not self.prefetch_adapters or rows >= 512 or i + 1 >= len(self.layers):
-            return False
-        nxt = self.layers[i + 1]
-        mods = (nxt.self_attn.qkv_proj, nxt.self_attn.o_proj, nxt.mlp.gate_up_proj, nxt.mlp.down_proj)
-        meta = mods[0]._runtime_metadata()
-        if meta is None or meta.no_lora_flag:
-            return False
-        if self._side_stream is None:
-            self._side_stream = torch.cuda.Stream(self.norm.device)
-        self._side_stream.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(self._side_stream):
-            LORA.prefetch_slabs([s for m in mods for s in (*m._a_slices(), *m._b_slices())], meta)
-        return True
-
     def _forward_fused(self, embeds, positions, step: AttentionStep):
         eps = self.cfg.rms_norm_eps
         slot_i32 = step.slot_mapping.to(torch.int32)
         hidden = embeds
         normed, _ = G.add_rms_norm(hidden, None, self.layers[0].input_layernorm, eps)
-        forked = False
         for i, layer in enumerate(self.layers):
-            forked = self._prefetch_next(i, embeds.size(0)) or forked
             attn = layer.self_attn.forward_fused(positions, normed, step, self.cos, self.sin, slot_i32)
             normed, hidden = G.add_rms_norm(attn, hidden, layer.post_attention_layernorm, eps)
             down = layer.mlp.down_proj(G.silu_and_mul(layer.mlp.gate_up_proj(normed)))
             following = self.layers[i + 1].input_layernorm if i + 1 < len(self.layers) else self.norm
             normed, hidden = G.add_rms_norm(down, hidden, following, eps)
-        if forked:
-            torch.cuda.current_stream().wait_stream(self._side_stream)
         return normed
 
     def forward(self, embeds, positions, step: AttentionStep):

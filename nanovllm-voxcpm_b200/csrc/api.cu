@@ -3,12 +3,10 @@
 #include "common.cuh"
 #include "generic.cuh"
 #include "bgmv_fused.cuh"
-#include "bgmv_split.cuh"
 #include "metadata.cuh"
 #include "tp_exchange.cuh"
 #include "slot_loader.cuh"
 #include "glue.cuh"
-#include "prefetch.cuh"
 #include "sgmv_tc.cuh"
 #include "gemm_tc.cuh"
 
@@ -94,9 +92,6 @@ int launch_generic_expand(void* y, int64_t y_ld, const void* tmp, int T_rows, co
 
 }  // namespace
 
-// 0 = row-split kernel when it takes the shape, else the column-split one; 1 / 2 force one of them
-static int g_decode_kernel = 0;
-
 extern "C" {
 
 int lora_b200_version(void) { return B200_LORA_ABI_VERSION; }
@@ -119,18 +114,8 @@ int lora_b200_set_option(int32_t key, int32_t value) {
     bgmv_options().ring_kb = value;
     return B200_LORA_OK;
   }
-  if (key == B200_LORA_OPT_DECODE_KERNEL) {
-    if (value < 0 || value > 2) return fail(B200_LORA_EINVAL, "decode kernel %d not in {0,1,2}", value);
-    g_decode_kernel = value;
-    return B200_LORA_OK;
-  }
   if (key == B200_LORA_OPT_KSPLIT) {
     bgmv_options().ksplit = value != 0;
-    return B200_LORA_OK;
-  }
-  if (key == B200_LORA_OPT_SMEM_KB) {
-    if (value < 0 || value > 227) return fail(B200_LORA_EINVAL, "shared-memory cap %d KB outside [0, 227]", value);
-    bgmv_split_options().smem_kb = value;
     return B200_LORA_OK;
   }
   return fail(B200_LORA_EINVAL, "unknown option %d", key);
@@ -170,13 +155,6 @@ int lora_b200_glue_rope_kv_store(void* qkv, int64_t qkv_ld, int32_t T, int32_t n
 int lora_b200_glue_silu_mul(void* out, int64_t out_ld, const void* gate_up, int64_t gate_up_ld, int32_t T,
                             int32_t intermediate, int32_t dtype, void* stream) {
   return silu_mul_launch(out, out_ld, gate_up, gate_up_ld, T, intermediate, dtype, static_cast<cudaStream_t>(stream));
-}
-
-int lora_b200_prefetch_slabs(const void* const* slabs, const int64_t* slot_stride_bytes, const int64_t* bytes_per_slot,
-                             int32_t n_slabs, const int32_t* slot_ids, const int32_t* counts, int32_t n_buckets, int32_t S,
-                             void* stream) {
-  return prefetch_slabs_launch(slabs, slot_stride_bytes, bytes_per_slot, n_slabs, slot_ids, counts, n_buckets, S,
-                               static_cast<cudaStream_t>(stream));
 }
 
 size_t lora_b200_tp_exchange_bytes(int32_t tp, int32_t capacity) { return tp_exchange_bytes(tp, capacity); }
@@ -352,7 +330,7 @@ static int add_or_delta(void* y, int64_t y_ld, const void* x, int64_t x_ld, int3
     bp.mode = 3;
     bp.token_to_slot = token_to_slot;
     const bool decode_like = T < kSgmvAutoMinTokens || T < 32 * n_buckets;
-    if (dtype == B200_LORA_BF16 && have_buckets && g_decode_kernel != 2 &&
+    if (dtype == B200_LORA_BF16 && have_buckets &&
         (impl == B200_LORA_IMPL_BGMV || (impl == B200_LORA_IMPL_AUTO && decode_like)) && bgmv_supported(bp, nullptr))
       return bgmv_launch(bp, st_);
     bp.mode = 0;
@@ -375,9 +353,7 @@ static int add_or_delta(void* y, int64_t y_ld, const void* x, int64_t x_ld, int3
     // batches to the fused kernel, everything else (other dtypes, odd shapes) to the generic one.
     int n_act = 0;
     for (int s = 0; s < st.n; ++s) n_act += st.out[s] > 0;
-    const bool bgmv_ok = dtype == B200_LORA_BF16 && have_buckets &&
-             (g_decode_kernel == 2 ? bgmv_split_supported(bp, nullptr)
-                                   : (bgmv_supported(bp, nullptr) || (g_decode_kernel == 0 && bgmv_split_supported(bp, nullptr))));
+    const bool bgmv_ok = dtype == B200_LORA_BF16 && have_buckets && bgmv_supported(bp, nullptr);
     // The prefill kernels tile rows in token order and pay one stage per run of equal slot, so they
     // want request-contiguous rows: with bucket arrays at hand, fewer than 32 rows per bucket on
     // average means a decode-like batch (slots scattered over the rows) and goes to the bucket kernel.
@@ -405,14 +381,7 @@ static int add_or_delta(void* y, int64_t y_ld, const void* x, int64_t x_ld, int3
       if (dtype != B200_LORA_BF16) return fail(B200_LORA_EUNSUPPORTED, "fused decode kernel is bf16 only");
       if (!have_buckets) return fail(B200_LORA_EINVAL, "fused decode kernel needs the bucket arrays");
       const char* why = nullptr;
-      if (g_decode_kernel == 2) {
-        if (!bgmv_split_supported(bp, &why)) return fail(B200_LORA_EUNSUPPORTED, "column-split decode kernel: %s", why);
-        return bgmv_split_launch(bp, st_);
-      }
-      // (mixing the two kernels per projection was measured slower than either alone: 7.99 vs 7.72 us)
       if (bgmv_supported(bp, &why)) return bgmv_launch(bp, st_);
-      const char* why_split = nullptr;
-      if (g_decode_kernel == 0 && bgmv_split_supported(bp, &why_split)) return bgmv_split_launch(bp, st_);
       return fail(B200_LORA_EUNSUPPORTED, "fused decode kernel: %s", why);
     }
     case B200_LORA_IMPL_SGMV:

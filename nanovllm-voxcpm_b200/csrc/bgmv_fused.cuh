@@ -398,11 +398,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
         if (tok0_hi >= 0) prefetch_l2(p.x + (int64_t)tok0_hi * p.x_ld + kc);
       }
     }
-#ifdef ABL_NOYPF
-    if (false) {
-#else
     if (!kOverwrite) {  // the lines of y that this thread's reductions will land in
-#endif
 #pragma unroll 1
       for (int e = 0; e < tiles_exp; ++e) {
         const int2 te = etab[e];
@@ -426,7 +422,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
   // all-gather item of this thread: one token row x four consecutive rank rows of this CTA
   const int groups = rows_c >> 2;
   const bool has_item = tid < kBgmvTok * groups;
-  const int it_tok = has_item ? tid / groups : 0;
+  const int it_tok = has_item ? tid / max(groups, 1) : 0;
   const int it_q = q_lo + 4 * (has_item ? tid - it_tok * groups : 0);
   const float* const red_rd = red + (size_t)it_tok * p.red_pitch + (it_q - q_lo);
   const uint32_t it_off = (uint32_t)(it_tok * p.pitchT + it_q * 2);
@@ -511,7 +507,6 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
         }
       };
       int j = 0;
-#ifndef BGMV_SHRINK_SINGLE
 #pragma unroll 1
       for (; j + 1 < nt_c; j += 2) {
         const int s0 = c_stage;
@@ -526,18 +521,17 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
         shrink_tiles_fn(std::integral_constant<int, 2>{}, j, a0, a1);
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(empty_bar(s0));
-          mbar_arrive(empty_bar(s1));
+          mbar_arrive_relaxed(empty_bar(s0));
+          mbar_arrive_relaxed(empty_bar(s1));
         }
       }
-#endif
 #pragma unroll 1
       for (; j < nt_c; ++j) {
         mbar_wait_bounded(full_bar(c_stage), c_parity, abort_flag);
         if (kp == 0 && j == 0 && pass == 0) { B200_TRACE_POINT(5) }
         shrink_tiles_fn(std::integral_constant<int, 1>{}, j, stage_addr, stage_addr);
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar(c_stage));
+        if (lane == 0) mbar_arrive_relaxed(empty_bar(c_stage));
         advance();
       }
     }
@@ -635,55 +629,39 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
     // ===== expand: y[tok, cols] += tmp[16 tok, r] . B_rows^T ======================
     // one tile of the ring per step: one 32-row block per warp (ER <= 256). Rows of a stage beyond the
     // tile's rows hold stale bytes; their products land in columns that are not written.
-    auto expand_fn = [&](int e, uint32_t addr0) {
-      constexpr int kTiles = 1;
-      const uint32_t addr1 = addr0;
-      int2 te[kTiles];
+    auto expand_fn = [&](int e, uint32_t tile_addr) {
+      const int2 te = etab[e];
+      float d[4][4];
 #pragma unroll
-      for (int u = 0; u < kTiles; ++u) te[u] = etab[e + u];
-      float d[kTiles][4][4];
-#pragma unroll
-      for (int u = 0; u < kTiles; ++u)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) d[u][j][0] = d[u][j][1] = d[u][j][2] = d[u][j][3] = 0.f;
+      for (int j = 0; j < 4; ++j) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.f;
+      const uint32_t a_addr = tmp_cur + t_off + (uint32_t)((te.y >> 16) * r_eff * 2);
+      const uint32_t w_addr = tile_addr + w_off;
 #pragma unroll 1
       for (int kb = 0; kb < kblocks; ++kb) {
+        const uint4 alo = lds128(a_addr + 64u * kb);
+        const uint4 ahi = lds128(a_addr + 64u * kb + 8u * (uint32_t)p.pitchT);
+        uint4 w[4];
 #pragma unroll
-        for (int u = 0; u < kTiles; ++u) {
-          const uint32_t a_addr = tmp_cur + t_off + (uint32_t)((te[u].y >> 16) * r_eff * 2) + 64u * kb;
-          const uint32_t w_addr = (u == 0 ? addr0 : addr1) + w_off + 64u * kb;
-          const uint4 alo = lds128(a_addr);
-          const uint4 ahi = lds128(a_addr + 8u * (uint32_t)p.pitchT);
-          uint4 w[4];
+        for (int j = 0; j < 4; ++j) w[j] = lds128(w_addr + 64u * kb + 2u * j * pitchB);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) w[j] = lds128(w_addr + 2u * j * pitchB);
+        for (int j = 0; j < 4; ++j) mma_bf16_16816(d[j], alo.x, ahi.x, alo.y, ahi.y, w[j].x, w[j].y);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) mma_bf16_16816(d[u][j], alo.x, ahi.x, alo.y, ahi.y, w[j].x, w[j].y);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) mma_bf16_16816(d[u][j], alo.z, ahi.z, alo.w, ahi.w, w[j].z, w[j].w);
-        }
+        for (int j = 0; j < 4; ++j) mma_bf16_16816(d[j], alo.z, ahi.z, alo.w, ahi.w, w[j].z, w[j].w);
       }
-#pragma unroll
-      for (int u = 0; u < kTiles; ++u) {
-        if (y_col < (te[u].y & 0xffff)) {
-          if (kOverwrite) {
-            if (tok_lo >= 0)
-              stg128(ylo_p + te[u].x, make_uint4(pack_bf16x2(d[u][0][0], d[u][0][1]), pack_bf16x2(d[u][1][0], d[u][1][1]),
-                                                 pack_bf16x2(d[u][2][0], d[u][2][1]), pack_bf16x2(d[u][3][0], d[u][3][1])));
-            if (tok_hi >= 0)
-              stg128(yhi_p + te[u].x, make_uint4(pack_bf16x2(d[u][0][2], d[u][0][3]), pack_bf16x2(d[u][1][2], d[u][1][3]),
-                                                 pack_bf16x2(d[u][2][2], d[u][2][3]), pack_bf16x2(d[u][3][2], d[u][3][3])));
-          } else {
-            // The delta is rounded to bf16 and added to y by one 16-byte reduction at the L2: y never
-            // travels to the SM and nothing waits for it. Each element of y receives exactly one
-            // reduction per launch, so the result does not depend on their order.
-            if (tok_lo >= 0)
-              red_add_bf16x8(ylo_p + te[u].x, pack_bf16x2(d[u][0][0], d[u][0][1]), pack_bf16x2(d[u][1][0], d[u][1][1]),
-                             pack_bf16x2(d[u][2][0], d[u][2][1]), pack_bf16x2(d[u][3][0], d[u][3][1]));
-            if (tok_hi >= 0)
-              red_add_bf16x8(yhi_p + te[u].x, pack_bf16x2(d[u][0][2], d[u][0][3]), pack_bf16x2(d[u][1][2], d[u][1][3]),
-                             pack_bf16x2(d[u][2][2], d[u][2][3]), pack_bf16x2(d[u][3][2], d[u][3][3]));
-          }
+      if (y_col < (te.y & 0xffff)) {
+        const uint4 lo4 = make_uint4(pack_bf16x2(d[0][0], d[0][1]), pack_bf16x2(d[1][0], d[1][1]),
+                                     pack_bf16x2(d[2][0], d[2][1]), pack_bf16x2(d[3][0], d[3][1]));
+        const uint4 hi4 = make_uint4(pack_bf16x2(d[0][2], d[0][3]), pack_bf16x2(d[1][2], d[1][3]),
+                                     pack_bf16x2(d[2][2], d[2][3]), pack_bf16x2(d[3][2], d[3][3]));
+        if (kOverwrite) {
+          if (tok_lo >= 0) stg128(ylo_p + te.x, lo4);
+          if (tok_hi >= 0) stg128(yhi_p + te.x, hi4);
+        } else {
+          // The delta is rounded to bf16 and added to y by one 16-byte reduction at the L2: y never
+          // travels to the SM and nothing waits for it. Each element of y receives exactly one
+          // reduction per launch, so the result does not depend on their order.
+          if (tok_lo >= 0) red_add_bf16x8(ylo_p + te.x, lo4.x, lo4.y, lo4.z, lo4.w);
+          if (tok_hi >= 0) red_add_bf16x8(yhi_p + te.x, hi4.x, hi4.y, hi4.z, hi4.w);
         }
       }
     };
@@ -695,7 +673,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
       expand_fn(e, stage_addr);
       if (pass == 0 && e < 10) { B200_TRACE_POINT(13 + 2 * e) }
       __syncwarp();
-      if (lane == 0) mbar_arrive(empty_bar(c_stage));
+      if (lane == 0) mbar_arrive_relaxed(empty_bar(c_stage));
       advance();
     }
     if (pass == 0) { B200_TRACE_POINT(10) }

@@ -99,7 +99,6 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tmap, uint3
                "r"(src_smem), "r"(c0), "r"(c1)
                : "memory");
 }
-__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_group_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");

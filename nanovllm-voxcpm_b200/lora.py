@@ -441,31 +441,3 @@ def install_into_reference(backend: LoRABackend | None = None) -> LoRABackend:
     backend = backend or B200LoRABackend()
     ref_lora.set_backend_for_testing(backend)
     return backend
-
-
-def prefetch_slabs(slabs, metadata: "LoRAMetadata") -> None:
-    """L2 prefetch hint (``lora_b200_prefetch_slabs``) for the slot regions of ``slabs`` (each ``[S, ...]``
-    contiguous, at most 16 per call) that the step's active buckets will read; launched on the current stream,
-    meant for a side stream one layer ahead of the launches that use the slabs. Needs the bucket arrays
-    (``active_slot_ids`` / ``num_tokens_per_slot``); without them nothing is launched."""
-    if not slabs:
-        return
-    ids, cnt = _i32(metadata.active_slot_ids, "slot ids"), _i32(metadata.num_tokens_per_slot, "counts")
-    if ids is None or cnt is None:
-        return
-    n_buckets = min(ids.numel(), cnt.numel())
-    if metadata.num_active_loras > 0:
-        n_buckets = min(n_buckets, metadata.num_active_loras)
-    if n_buckets <= 0:
-        return
-    N.require_cuda(*slabs, ids, cnt)
-    S = slabs[0].size(0)
-    for t in slabs:
-        if not t.is_contiguous() or t.size(0) != S:
-            raise ValueError("slabs must be contiguous [S, ...] tensors over the same slots")
-    import ctypes
-
-    strides = (ctypes.c_int64 * len(slabs))(*[t.stride(0) * t.element_size() for t in slabs])
-    with N.on_device(ids.device):
-        N.check(N.lib().lora_b200_prefetch_slabs(N.ptr_array(slabs), strides, strides, len(slabs), ids.data_ptr(),
-                                                 cnt.data_ptr(), n_buckets, S, N.current_stream(ids.device)))

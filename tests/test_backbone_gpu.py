@@ -97,24 +97,6 @@ def test_fused_glue_step_matches_the_torch_glue_step():
     torch.testing.assert_close(fused_graph, plain_decode, atol=3e-2, rtol=3e-2)
 
 
-def test_adapter_prefetch_changes_no_result():
-    """The L2 prefetch hint of the next layer's adapter weights (side stream, inside the captured graph) only moves
-    data closer: decode outputs are bit-identical with and without it."""
-    model, work = _model_and_work()
-    outs = {}
-    try:
-        model.fused_glue = True
-        for flag in (False, True):
-            model.prefetch_adapters = flag
-            run = BB.BackboneRunner(model, work, use_lora=True)
-            run.prefill()
-            run.decode(3, use_graph=True)
-            outs[flag] = run.last_output.float().cpu()
-    finally:
-        model.fused_glue = model.prefetch_adapters = False
-    assert torch.equal(outs[False], outs[True])
-
-
 def test_lora_first_order_in_the_decode_graph():
     """Decode steps with the delta written before the base GEMM (layers.LORA_FIRST): graph replay equals eager
     launches bit for bit, and the result stays within the stack's tolerance of the add-after-GEMM order."""

@@ -21,7 +21,7 @@ NEG_ZERO = -32768  # 0x8000 as int16
 @pytest.fixture(autouse=True)
 def _clean():
     CTX.reset_lora_context()
-    for key in (N.OPT_CLUSTER, N.OPT_RING_KB, N.OPT_DECODE_KERNEL, N.OPT_SMEM_KB):
+    for key in (N.OPT_CLUSTER, N.OPT_RING_KB):
         N.set_option(key, 0)
     N.set_option(N.OPT_PDL, 1)
     yield

@@ -29,8 +29,7 @@ def _clean():
     yield
     N.set_option(N.OPT_CLUSTER, 0)
     N.set_option(N.OPT_PDL, 1)
-    N.set_option(N.OPT_DECODE_KERNEL, N.DECODE_AUTO)
-    N.set_option(N.OPT_SMEM_KB, 0)
+    N.set_option(N.OPT_KSPLIT, 1)
     CTX.reset_lora_context()
     assert N.device_status() == 0, "a kernel gave up a bounded wait"
 
@@ -108,50 +107,6 @@ def test_bgmv_cluster_sizes(cluster, pdl):
         p = W.decode_projection(name, seed=3, T=96, S=8)
         out, y_in = run_add(p, N.IMPL_BGMV, "graph")
         check_against_oracle(p, out, y_in, what=f"{name}/C{cluster}/pdl{pdl}")
-
-
-@pytest.mark.parametrize("cluster", [0, 1, 2, 8])
-@pytest.mark.parametrize("smem_kb", [0, 227])
-def test_column_split_decode_kernel(cluster, smem_kb):
-    """The second fused decode kernel (input columns split over the cluster, st.async exchange,
-    two CTAs per SM): same contract, same oracle, every projection shape and bucket convention."""
-    N.set_option(N.OPT_DECODE_KERNEL, N.DECODE_COLUMN_SPLIT)
-    N.set_option(N.OPT_CLUSTER, cluster)
-    N.set_option(N.OPT_SMEM_KB, smem_kb)
-    for name, convention in (("qkv", "graph"), ("o", "eager"), ("gate_up", "vllm"), ("down", "graph")):
-        if cluster == 8 and name == "qkv":
-            continue  # 8 receive buffers of 96 rank rows exceed the shared memory of one CTA
-        p = W.decode_projection(name, seed=11)
-        out, y_in = run_add(p, N.IMPL_BGMV, convention)
-        check_against_oracle(p, out, y_in, what=f"column-split/{name}/C{cluster}")
-        out2, _ = run_add(p, N.IMPL_BGMV, convention)
-        assert torch.equal(out.view(torch.int16), out2.view(torch.int16)), "two runs differ bitwise"
-    # 7 passes of 16 tokens per bucket (receive buffer reused under the peers' free signal), one token,
-    # ragged widths, rank 128 with a rank array, scales
-    p = W.make_projection(5, 200, 1024, [1024, 128, 128], 2, 32, p_none=0.2)
-    out, y_in = run_add(p, N.IMPL_BGMV)
-    check_against_oracle(p, out, y_in, what="column-split/many tokens")
-    p = W.make_projection(6, 1, 1024, [1024], 4, 32, token_to_slot=[3])
-    out, y_in = run_add(p, N.IMPL_BGMV)
-    check_against_oracle(p, out, y_in, what="column-split/one token")
-    p = W.make_projection(11, 37, 1312, [200, 40], 3, 32)
-    out, y_in = run_add(p, N.IMPL_BGMV, y_pad=8, x_pad=16)
-    check_against_oracle(p, out, y_in, what="column-split/ragged")
-    if cluster != 8:
-        sps = torch.tensor([1.0, 0.5, 2.0])
-        p = W.make_projection(12, 40, 512, [512], 3, 128, ranks=[128, 40, 8])
-        out, y_in = run_add(p, N.IMPL_BGMV, use_ranks=True, scaling=0.5, scale_per_slot=sps)
-        check_against_oracle(p, out, y_in, 0.5, sps, what="column-split/r128")
-
-
-def test_column_split_unsupported_shapes_fall_back_or_report():
-    p = W.make_projection(9, 70, 2048, [2048, 256, 256], 6, 64, p_none=0.15)  # 3 slices x rank 64: 6 row boxes
-    N.set_option(N.OPT_DECODE_KERNEL, N.DECODE_COLUMN_SPLIT)
-    with pytest.raises(RuntimeError, match="column-split"):
-        run_add(p, N.IMPL_BGMV)
-    N.set_option(N.OPT_DECODE_KERNEL, N.DECODE_AUTO)
-    out, y_in = run_add(p, N.IMPL_BGMV)
-    check_against_oracle(p, out, y_in, what="auto picks the row-split kernel")
 
 
 def test_bgmv_many_tokens_per_slot_and_single_token():
@@ -462,22 +417,47 @@ def test_sgmv_random_slots_and_full_size_properties():
     p = W.make_projection(23, 200, 256, [256], 8, 32, p_none=0.2)
     out, y_in = run_add(p, N.IMPL_SGMV)
     check_against_oracle(p, out, y_in, what="sgmv random slots")
-    # full prefill size (8192 rows): linearity of the delta in x, checked without the oracle
-    big = W.prefill_projection("o", seed=0).to_device(DEV)
-    S = big.a_slabs[0].shape[0]
-    meta = metadata_for(big.token_to_slot, "eager", S)
-    zeros = torch.zeros_like(big.y)
-    y1, y2 = zeros.clone(), zeros.clone()
-    LORA.launch_add(y1, big.x, big.a_slabs, big.b_slabs, big.out_sizes, big.col_offsets, meta, 1.0, impl=N.IMPL_SGMV)
-    LORA.launch_add(y2, big.x * 2, big.a_slabs, big.b_slabs, big.out_sizes, big.col_offsets, meta, 1.0, impl=N.IMPL_SGMV)
+
+
+@pytest.mark.parametrize("name", ["qkv", "o", "gate_up", "down"])
+def test_prefill_config_full_size_matches_oracle(name):
+    """The prefill configuration at its full size (16 requests packed to 8172 rows, hidden 2048, intermediate
+    6144, ranks 8 / 16 / 64 in rank-64 slabs): the tensor-core add, the overwrite form and the fused base GEMM
+    against the fp32 oracle, rows without adapter bit-exact in all three."""
+    p = W.prefill_projection(name, seed=0)
+    assert p.x.shape[0] > 8000
+    p.token_to_slot[300:391] = -1  # a hole without adapter across a 128-row block boundary
+    p.token_to_slot[-17:] = -1     # and a ragged tail
+    none = p.token_to_slot < 0
+    # --- y += delta
+    out, y_in = run_add(p, N.IMPL_SGMV)
+    check_against_oracle(p, out, y_in, what=f"sgmv add / {name} / full size")
+    # --- y = delta (-0.0 in rows without adapter)
+    d = p.to_device(DEV)
+    S = d.a_slabs[0].shape[0]
+    delta = torch.full_like(d.y, 7.0)
+    LORA.launch_add(delta, d.x, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets, metadata_for(d.token_to_slot, "eager", S),
+                    1.0, impl=N.IMPL_SGMV, overwrite=True)
     torch.cuda.synchronize()
-    assert float(y1.float().abs().max()) > 0
-    torch.testing.assert_close(y2.float(), 2 * y1.float(), atol=2e-2, rtol=2e-2)
-    # and against the fused decode kernel on the same full-size input (independent implementation)
-    y3 = zeros.clone()
-    LORA.launch_add(y3, big.x, big.a_slabs, big.b_slabs, big.out_sizes, big.col_offsets, meta, 1.0, impl=N.IMPL_BGMV)
+    want = O.add_lora(torch.zeros_like(p.y), p.x, p.a_slabs, p.b_slabs, p.token_to_slot, 1.0, p.col_offsets)
+    assert_lora_close(delta.cpu(), want, what=f"sgmv delta / {name} / full size")
+    assert bool((delta.cpu()[none].view(torch.int16) == -32768).all()), "rows without adapter are not -0.0"
+    # --- y = x @ W.T + delta in one kernel
+    gen = torch.Generator().manual_seed(99)
+    weight = (torch.randn(sum(p.out_sizes), p.x.shape[1], generator=gen) * 0.02).to(torch.bfloat16)
+    base = p.x.float() @ weight.float().T
+    ref = O.add_lora(base, p.x, p.a_slabs, p.b_slabs, p.token_to_slot, 1.0, p.col_offsets)
+    w_dev = weight.to(DEV)
+    fused = LORA.linear_lora(d.x, w_dev, None, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets, d.token_to_slot, 1.0)
+    plain = LORA.linear_lora(d.x, w_dev, None, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets, None, 1.0)
     torch.cuda.synchronize()
-    assert_lora_close(y1, y3.float(), what="sgmv vs fused decode kernel at 8192 rows")
+    assert N.device_status(reset=True) == 0
+    assert_lora_close(fused.cpu(), ref, max_abs=4e-2, what=f"fused linear / {name} / full size")  # base rounding included
+    assert_lora_close(plain.cpu(), base, max_abs=4e-2, what=f"plain linear / {name} / full size")
+    none_d = none.to(DEV)
+    assert torch.equal(fused[none_d].view(torch.int16), plain[none_d].view(torch.int16)), "rows with slot -1 changed"
+    # the delta alone (fused minus plain, both rounded once) at the path's own tolerance
+    assert_lora_close((fused.float() - plain.float()).cpu(), want, max_abs=3e-2, what=f"fused delta / {name}")
 
 
 def test_sgmv_unsupported_and_workspace_errors():
