@@ -330,6 +330,7 @@ int lora_b200_shrink_allreduce_expand(void* y, int64_t y_ld, const void* x, int6
 #define B200_LORA_OPT_CLUSTER 1 /* CTAs per slot bucket: 1, 2, 4, 8; 0 = choose from n_buckets */
 #define B200_LORA_OPT_PDL 2     /* 1 = launch with programmatic stream serialization (default), 0 = off */
 #define B200_LORA_OPT_RING_KB 3 /* cap of the shared-memory stage ring in KB, 0 = as large as fits */
+#define B200_LORA_OPT_PEER_POLL_LIMIT 7 /* tensor-parallel exchange: polls of a peer's flag after which the wait gives up and bit 2 of the device status word is set; 0 = default (about a second) */
 #define B200_LORA_OPT_KSPLIT 6 /* fused decode kernel: 1 = deal the K parts of long input rows (>= 1024 columns per CTA of a cluster) over the cluster (default), 0 = always split the rank rows */
 
 /* Sets a tuning knob; returns 0, or B200_LORA_EINVAL for an unknown key / value.

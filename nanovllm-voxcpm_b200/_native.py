@@ -95,7 +95,7 @@ _SIGNATURES = {
     "lora_b200_device_status": (c_int32, [POINTER(c_int32), c_int32]),
 }
 
-OPT_CLUSTER, OPT_PDL, OPT_RING_KB, OPT_KSPLIT = 1, 2, 3, 6
+OPT_CLUSTER, OPT_PDL, OPT_RING_KB, OPT_KSPLIT, OPT_PEER_POLL_LIMIT = 1, 2, 3, 6, 7
 META_GRAPH, META_KERNEL, META_EAGER = 0, 1, 2
 
 

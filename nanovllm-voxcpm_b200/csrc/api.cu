@@ -114,6 +114,11 @@ int lora_b200_set_option(int32_t key, int32_t value) {
     bgmv_options().ring_kb = value;
     return B200_LORA_OK;
   }
+  if (key == B200_LORA_OPT_PEER_POLL_LIMIT) {
+    if (value < 0) return fail(B200_LORA_EINVAL, "poll limit %d is negative", value);
+    tp_spin_limit() = value == 0 ? kTpSpinLimit : value;
+    return B200_LORA_OK;
+  }
   if (key == B200_LORA_OPT_KSPLIT) {
     bgmv_options().ksplit = value != 0;
     return B200_LORA_OK;
@@ -239,10 +244,15 @@ int lora_b200_shrink_allreduce_expand(void* y, int64_t y_ld, const void* x, int6
   SliceTable st;
   if (int rc = fill_slices(st, n_slices, a_slabs, b_slabs, out_sizes, col_offsets, true, true)) return rc;
   int n_act = 0;
+  int64_t width = 0;
   for (int s = 0; s < st.n; ++s) {
     if (st.out[s] == 0) return fail(B200_LORA_EUNSUPPORTED, "tensor-parallel exchange: zero-width slice %d", s);
+    width = width > (int64_t)st.col[s] + st.out[s] ? width : (int64_t)st.col[s] + st.out[s];
     ++n_act;
   }
+  if (y_ld < width || x_ld < in_dim)
+    return fail(B200_LORA_EINVAL, "row stride smaller than row: y_ld=%lld (need %lld) x_ld=%lld (need %d)",
+                (long long)y_ld, (long long)width, (long long)x_ld, in_dim);
   const int64_t count64 = (int64_t)n_act * T * r_max;
   if (count64 > (int64_t)INT32_MAX || (count64 & 3)) return fail(B200_LORA_EINVAL, "n_slices * T * r_max must be a multiple of 4 below 2^31");
   const int count = (int)count64;

@@ -475,7 +475,7 @@ inline int tc_tile_launch(const GemmMaps& maps, const GemmArgs& a, cudaStream_t 
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = bgmv_options().pdl ? 1 : 0;  // B200_LORA_OPT_PDL = 0: strict stream order
   cudaError_t e = cudaLaunchKernelEx(&cfg, tc_tile_kernel, maps, a);
   if (e != cudaSuccess) {
     cudaGetLastError();

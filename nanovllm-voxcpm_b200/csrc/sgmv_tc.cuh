@@ -14,6 +14,7 @@
 #pragma once
 
 #include "tc_common.cuh"
+#include "bgmv_fused.cuh"  // launch options shared by all kernels (programmatic dependent launch on / off)
 
 namespace b200lora {
 
@@ -495,7 +496,7 @@ inline int sgmv_launch_shrink(const SgmvMaps& maps, const SgmvArgs& a_in, cudaSt
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = bgmv_options().pdl ? 1 : 0;  // B200_LORA_OPT_PDL = 0: strict stream order (the waits in the kernel are then no-ops)
   cudaError_t e = cudaLaunchKernelEx(&cfg, sgmv_shrink_kernel, maps, a);
   if (e != cudaSuccess) {
     cudaGetLastError();

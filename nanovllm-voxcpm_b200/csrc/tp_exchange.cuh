@@ -30,7 +30,13 @@ constexpr int kTpMaxRanks = 8;
 constexpr int kTpMaxCtas = 64;
 constexpr int kTpThreads = 256;
 constexpr int kStatusPeerWaitGaveUp = 2;
-constexpr int kTpSpinLimit = 1 << 21;  // polls of a system-scope load: about a second
+constexpr int kTpSpinLimit = 1 << 21;  // default poll limit of a system-scope load: about a second
+
+// polls after which the wait for a peer's flag gives up (lora_b200_set_option, B200_LORA_OPT_PEER_POLL_LIMIT)
+inline int& tp_spin_limit() {
+  static int limit = kTpSpinLimit;
+  return limit;
+}
 
 struct TpExchangeArgs {
   const float* partial;  // [count] this rank's partial sums
@@ -39,6 +45,7 @@ struct TpExchangeArgs {
   int* flags[kTpMaxRanks];
   int* state;
   int rank, tp, count, capacity, n_cta;
+  int spin_limit;  // polls of a peer's flag before the wait gives up
 };
 
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
@@ -77,7 +84,7 @@ __global__ void __launch_bounds__(kTpThreads) tp_allreduce_kernel(const TpExchan
     const int* f = a.flags[a.rank] + ((size_t)par * a.tp + tid) * kTpMaxCtas + cta;
     int it = 0;
     while (ld_acquire_sys(f) != epoch) {
-      if (++it >= kTpSpinLimit) { gave_up = 1; break; }
+      if (++it >= a.spin_limit) { gave_up = 1; break; }
     }
   }
   __syncthreads();
@@ -130,6 +137,7 @@ inline int tp_allreduce_launch(const float* partial, float* out, int count, void
   }
   a.state = reinterpret_cast<int*>(static_cast<uint8_t*>(peer_buffers[rank]) + tp_state_offset(tp, capacity));
   a.n_cta = std::max(1, std::min(kTpMaxCtas, (count * 4 + 16383) / 16384));
+  a.spin_limit = tp_spin_limit();
   tp_allreduce_kernel<<<a.n_cta, kTpThreads, 0, stream>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_LORA_ECUDA, "tp_allreduce_kernel launch: %s", cudaGetErrorString(e));

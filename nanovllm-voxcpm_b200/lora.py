@@ -103,15 +103,29 @@ def _i32(t: torch.Tensor | None, name: str) -> torch.Tensor | None:
 SGMV_MIN_TOKENS = 512
 
 _SCRATCH: dict[torch.device, torch.Tensor] = {}
+#: buffers that were replaced by a larger one: a CUDA graph captured earlier may still write through their
+#: addresses, so they are kept for the life of the process instead of going back to the allocator
+_RETIRED_SCRATCH: list[torch.Tensor] = []
+
+
+def reserve_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Sizes the per-device scratch buffer up front (e.g. from ``max_num_batched_tokens`` x slices x
+    ``max_lora_rank`` before CUDA graphs are captured), so that it never has to grow later."""
+    return scratch_for(torch.device(device), int(nbytes))
 
 
 def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Grow-only per-device scratch buffer for the prefill kernels' rank-r intermediate.
+    """Per-device scratch buffer for the prefill kernels' rank-r intermediate.
 
-    The reference allocates this intermediate on every call (``lora.py:302``); here one buffer
-    per device is reused, so steady-state calls (and CUDA-graph replays) allocate nothing."""
+    The reference allocates this intermediate on every call (``lora.py:302``); here one buffer per device
+    is reused, so steady-state calls (and CUDA-graph replays) allocate nothing. The buffer only grows, and a
+    buffer that is outgrown is never freed: its address may be baked into a captured graph. One buffer per
+    device means one stream at a time may run calls that use it (the runner's single stream); callers that
+    overlap streams pass their own ``workspace``."""
     buf = _SCRATCH.get(device)
     if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            _RETIRED_SCRATCH.append(buf)
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _SCRATCH[device] = buf
     return buf

@@ -8,10 +8,17 @@ shrinks on its input shard, the ``[n, T, r]`` partials are summed here, and each
 its ``out / tp`` columns of ``lora_B``; the base output's own ``[T, out]`` all-reduce
 (``nanovllm_voxcpm/layers/lora.py:722-742``) then assembles the full delta exactly once.
 
-Every rank must issue the same sequence of exchanges. Multicast is not used (plain peer stores).
+Every rank must issue the same sequence of exchanges. Multicast is not used: the kernel issues plain peer
+stores, and the symmetric allocation is made with ``TORCH_SYMM_MEM_DISABLE_MULTICAST=1`` (set here before
+torch's symmetric memory is first imported), so that the buffer is never bound to an NVLink multicast object -
+a rank that dies while its memory is bound to one can fault its peers.
 """
 
 from __future__ import annotations
+
+import os
+
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 import torch
 import torch.distributed as dist
@@ -34,7 +41,14 @@ class TpExchange:
         self._buffer.zero_()
         torch.cuda.synchronize(self.device)
         self._handle = symm_mem.rendezvous(self._buffer, group=self.group)
+        mc = getattr(self._handle, "multicast_ptr", 0)
+        if mc not in (0, None):
+            raise RuntimeError("the exchange buffer was bound to an NVLink multicast object; set "
+                               "TORCH_SYMM_MEM_DISABLE_MULTICAST=1 before torch.distributed._symmetric_memory is imported")
         self._peers = (N.c_void_p * self.tp)(*[int(p) for p in self._handle.buffer_ptrs])
+        #: fp32 intermediate of shrink_allreduce_expand: owned here, fixed size, so an address captured in a
+        #: CUDA graph stays valid however the shared scratch of other calls grows
+        self._tmp = torch.empty(self.capacity * 4 + 256, dtype=torch.uint8, device=self.device)
         dist.barrier(self.group)  # every rank's buffer is zeroed and mapped before the first push
 
     def all_reduce_(self, partial: torch.Tensor) -> torch.Tensor:
@@ -83,7 +97,7 @@ def shrink_allreduce_expand(y, x, a_slabs, b_slabs, out_sizes, col_offsets, meta
     if n_buckets <= 0:
         srt = ids = cnt = off = None
         n_buckets = 0
-    tmp = scratch_for(x.device, n * T * r_max * 4 + 256)
+    tmp = exchange._tmp if exchange is not None and n * T * r_max <= exchange.capacity else scratch_for(x.device, n * T * r_max * 4 + 256)
     tmp_ptr = (tmp.data_ptr() + 255) & ~255
     with N.on_device(x.device):
         N.check(N.lib().lora_b200_shrink_allreduce_expand(

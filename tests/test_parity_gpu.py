@@ -442,9 +442,10 @@ def test_prefill_config_full_size_matches_oracle(name):
     want = O.add_lora(torch.zeros_like(p.y), p.x, p.a_slabs, p.b_slabs, p.token_to_slot, 1.0, p.col_offsets)
     assert_lora_close(delta.cpu(), want, what=f"sgmv delta / {name} / full size")
     assert bool((delta.cpu()[none].view(torch.int16) == -32768).all()), "rows without adapter are not -0.0"
-    # --- y = x @ W.T + delta in one kernel
+    # --- y = x @ W.T + delta in one kernel; the base weight is scaled so that outputs stay of order one
+    #     (|y| < 4) and the path's own absolute bound is the one tested, rounding of the base included
     gen = torch.Generator().manual_seed(99)
-    weight = (torch.randn(sum(p.out_sizes), p.x.shape[1], generator=gen) * 0.02).to(torch.bfloat16)
+    weight = (torch.randn(sum(p.out_sizes), p.x.shape[1], generator=gen) * (0.5 / p.x.shape[1] ** 0.5)).to(torch.bfloat16)
     base = p.x.float() @ weight.float().T
     ref = O.add_lora(base, p.x, p.a_slabs, p.b_slabs, p.token_to_slot, 1.0, p.col_offsets)
     w_dev = weight.to(DEV)
@@ -452,12 +453,12 @@ def test_prefill_config_full_size_matches_oracle(name):
     plain = LORA.linear_lora(d.x, w_dev, None, d.a_slabs, d.b_slabs, d.out_sizes, d.col_offsets, None, 1.0)
     torch.cuda.synchronize()
     assert N.device_status(reset=True) == 0
-    assert_lora_close(fused.cpu(), ref, max_abs=4e-2, what=f"fused linear / {name} / full size")  # base rounding included
-    assert_lora_close(plain.cpu(), base, max_abs=4e-2, what=f"plain linear / {name} / full size")
+    assert float(ref.abs().max()) < 4.0
+    assert_lora_close(fused.cpu(), ref, what=f"fused linear / {name} / full size")
+    assert_lora_close(plain.cpu(), base, what=f"plain linear / {name} / full size")
     none_d = none.to(DEV)
     assert torch.equal(fused[none_d].view(torch.int16), plain[none_d].view(torch.int16)), "rows with slot -1 changed"
-    # the delta alone (fused minus plain, both rounded once) at the path's own tolerance
-    assert_lora_close((fused.float() - plain.float()).cpu(), want, max_abs=3e-2, what=f"fused delta / {name}")
+    assert not torch.equal(fused[~none_d], plain[~none_d])
 
 
 def test_sgmv_unsupported_and_workspace_errors():

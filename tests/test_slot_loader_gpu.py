@@ -10,6 +10,7 @@ from nanovllm_voxcpm_b200 import _native as N
 from nanovllm_voxcpm_b200 import backbone as BB
 from nanovllm_voxcpm_b200 import layers as L
 from nanovllm_voxcpm_b200.slot_loader import SlotLoader
+from oracle import lora_oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -71,7 +72,19 @@ def test_batched_slot_load_equals_module_by_module_load():
         (0, _adapter(model, 4, 0.5, seed=4, dtype=torch.float16)),
     ]
     cleared_by_runner = {}
+    # third witness: the oracle's slab writer on host copies of the (all-zero) slabs
+    lora_mods = {n: m for n, m in model.named_modules() if isinstance(m, L._LORA_LAYER_TYPES)}
+    oracle_slabs = {n: ([torch.zeros_like(t, device="cpu") for t in m._a_slices()],
+                        [torch.zeros_like(t, device="cpu") for t in m._b_slices()]) for n, m in lora_mods.items()}
     for slot, payload in steps:
+        for name in cleared_by_runner.get(slot, []):
+            for t in (*oracle_slabs[name][0], *oracle_slabs[name][1]):
+                t[slot].zero_()
+        for name, (a, b, rank, sc) in payload.items():
+            a_list = list(a) if isinstance(b, list) else [a]
+            b_list = b if isinstance(b, list) else [b]
+            for a_slab, b_slab, a_i, b_i in zip(*oracle_slabs[name], a_list, b_list):
+                O.write_slot(a_slab, b_slab, slot, a_i, b_i, rank, sc)
         loader.load_slot(slot, payload)
         # the reference path: clear what the previous occupant loaded, then module by module
         for name in cleared_by_runner.get(slot, []):
@@ -85,6 +98,9 @@ def test_batched_slot_load_equals_module_by_module_load():
                 assert got[key] == want[key], key
             else:
                 assert torch.equal(got[key], want[key]), f"{key} differs after loading slot {slot}"
+        for name, m in lora_mods.items():
+            for i, (t, want_t) in enumerate(zip((*m._a_slices(), *m._b_slices()), (*oracle_slabs[name][0], *oracle_slabs[name][1]))):
+                assert torch.equal(t.cpu(), want_t), f"{name} slab {i} differs from the oracle's writer after loading slot {slot}"
     assert N.device_status() == 0
     with pytest.raises(ValueError, match="Unknown LoRA target module"):
         loader.load_slot(0, {"nope": steps[0][1][next(iter(steps[0][1]))]})
