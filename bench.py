@@ -68,7 +68,13 @@ def parse_args():
                          "accumulates into it (first), or added after the GEMM as the reference does (after)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "linear", "backbone", "tp", "admission", "glue"],
+    ap.add_argument("--parallelism", default="tp", choices=["tp", "replicas"],
+                    help="--workload backbone5 under torchrun: one tensor-parallel group, or one replica per GPU")
+    ap.add_argument("--slab-gb", type=float, default=80.0, help="--workload backbone5: HBM budget of the adapter slabs per GPU")
+    ap.add_argument("--no-base", action="store_true", help="--workload backbone5: skip the run without adapters")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="decode workload: only the headline measurement (no secondary / reference_gpu / backbone / tp blocks)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "linear", "backbone", "backbone5", "tp", "admission", "glue"],
                     help="decode = the headline decode BGMV layer; prefill = prefill SGMV add (tcgen05 kernels) of one "
                          "layer; linear = base GEMM + LoRA in one tensor-core kernel for the same layer; backbone = whole "
                          "decoder steps (prefill + graph-replayed decode) around the LoRA linears")
@@ -223,6 +229,26 @@ class ClockSampler:
         return out
 
 
+def bind_to_gpu_cpus(index):
+    """Pins this process to the CPUs that NVML reports as closest to GPU `index` (its NUMA node), so that pinned
+    host buffers and the copy engines' traffic stay on that node. A setting of this process only. Returns a
+    short description for the JSON line."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return "no CPU of the GPU's node is available to this process"
+        os.sched_setaffinity(0, cpus)
+        return f"{len(cpus)} CPUs of the GPU's NUMA node"
+    except Exception as exc:  # NVML missing or not permitted: run unbound
+        return f"unbound ({type(exc).__name__})"
+
+
 def build_gpu_workload(device, layers):
     """Per layer and projection: device-resident x, y, slabs (distinct per layer)."""
     from nanovllm_voxcpm_b200 import workloads as W
@@ -267,8 +293,9 @@ def run_gpu_arm(args):
         raise RuntimeError("bench.py needs a CUDA device: the product has no CPU path (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    binding = bind_to_gpu_cpus(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        _init_dist(device)
     backend = LORA.B200LoRABackend()
     status = backend.availability()
     if not status.available:
@@ -349,12 +376,20 @@ def run_gpu_arm(args):
         # Host side of a step: per layer ONE pinned staging buffer holding x and y of its projections
         # (x block first, then the y block), mirrored by one device buffer whose slices the LoRA calls
         # use; a layer costs one host->device copy (x and y) and one device->host copy (the y block).
+        # All host buffers of a rank are slices of ONE pinned arena (inputs first, then outputs).
+        n_in = sum(p["x"].numel() + p["y"].numel() for layer in work for p in layer)
+        n_out = sum(p["y"].numel() for layer in work for p in layer)
+        arena = torch.empty(n_in + n_out, dtype=torch.bfloat16).pin_memory()
+        cursor = {"in": 0, "out": n_in}
+
         def packed_layer(layer):
             nx = sum(p["x"].numel() for p in layer)
             ny = sum(p["y"].numel() for p in layer)
             dev = torch.empty(nx + ny, dtype=torch.bfloat16, device=device)
-            hst = torch.empty(nx + ny, dtype=torch.bfloat16).pin_memory()
-            out = torch.empty(ny, dtype=torch.bfloat16).pin_memory()
+            hst = arena[cursor["in"]: cursor["in"] + nx + ny]
+            out = arena[cursor["out"]: cursor["out"] + ny]
+            cursor["in"] += nx + ny
+            cursor["out"] += ny
             views, ox, oy = [], 0, nx
             for p in layer:
                 xv = dev[ox: ox + p["x"].numel()].view_as(p["x"])
@@ -416,8 +451,44 @@ def run_gpu_arm(args):
             e2e_ms = float(t.item())
         del eager_meta
         e2e = {"value": bytes_per_step * world / (e2e_ms / n_e2e * 1e-3) / 1e9, "unit": "GB/s",
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / n_e2e, "steps": n_e2e}
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / n_e2e, "steps": n_e2e,
+               # what one rank moves over its host link per second (both directions), and what bound it to its CPUs
+               "per_rank_host_link_gbs": (h2d + d2h) / (e2e_ms / n_e2e * 1e-3) / 1e9,
+               "per_rank_value": bytes_per_step / (e2e_ms / n_e2e * 1e-3) / 1e9, "cpu_binding": binding}
 
+    # ---- further blocks of the same line (skipped by --no-extras and in tuning runs of a subset) --------------
+    extras = {}
+    if not args.no_extras and args.only is None and args.layers == N_LAYERS and graph is not None:
+        import copy
+
+        def guarded(fn):
+            try:
+                return fn()
+            except Exception as exc:  # a block that cannot run is reported, the headline stays
+                return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+
+        def brief(line, keys):
+            return {k: line[k] for k in keys if k in line} if "unavailable" not in line else line
+
+        if world == 1:
+            # the tensor-core kernels: prefill add (HBM-bound) and fused base GEMM + LoRA (tensor-bound)
+            sec = {}
+            for wl in ("prefill", "linear"):
+                a2 = copy.copy(args)
+                a2.workload, a2.only, a2.steps, a2.warmup = wl, None, 10, 3
+                sec[wl] = guarded(lambda a2=a2: brief(run_prefill_arm(a2, emit=False),
+                                                      ("metric", "value", "unit", "ms_per_step", "roofline", "us_per_projection",
+                                                       "clocks", "cublas_plus_prefill_add_ms_per_step", "lora_tflops")))
+            extras["secondary"] = sec
+            # the incumbent on the same GPU and inputs: the unmodified reference package's own Triton backend
+            a3 = copy.copy(args)
+            a3.workload, a3.only, a3.steps, a3.warmup = "decode", None, 10, 3
+            extras["reference_gpu"] = guarded(lambda: brief(run_reference_gpu_arm(a3, emit=False),
+                                                            ("value", "unit", "ms_per_step", "us_per_projection_call", "launch_mode",
+                                                             "backend", "unavailable")))
+        extras["backbone"] = guarded(lambda: backbone_replicas_block(device, world))
+        if world > 1:
+            extras["tp"] = guarded(lambda: tp_block(device, world, rank))
     status_word = N.device_status()
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -450,13 +521,14 @@ def run_gpu_arm(args):
                 "sample": f"one layer (4 projections, {r['bytes'] / 1e6:.1f} MB algorithmic) x {r['iters']} iterations, "
                           f"fp32 torch CPU per-slot formula, median {r['ms']:.2f} ms",
             }
+        line.update(extras)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
 
 # ------------------------------------------------------------------ secondary workloads (prefill kernels)
-def run_prefill_arm(args):
+def run_prefill_arm(args, emit=True):
     """One step = the four multi-LoRA projections of one prefill layer (16 requests, <= 8192 rows, hidden 2048,
     intermediate 6144, ranks 8/16/64 in a rank-64 slab). `prefill`: y += delta through lora_b200_add
     (tcgen05 shrink + tile / run expand), HBM-bound. `linear`: y = x W^T + delta through lora_b200_linear_lora,
@@ -591,11 +663,13 @@ def run_prefill_arm(args):
                                   "kernel": "sgmv_shrink_kernel + tc_tile_kernel",
                                   "algorithmic_bytes_per_step": bytes_step},
                      "lora_tflops": lora_flops / (ms_per_step * 1e-3) / 1e12})
-    print(json.dumps(line))
+    if emit:
+        print(json.dumps(line))
+    return line
 
 
 # ------------------------------------------------------------------ the reference's own GPU backend
-def run_reference_gpu_arm(args):
+def run_reference_gpu_arm(args, emit=True):
     """Times `get_backend().add_lora` of the UNMODIFIED reference package (installed from its source tree into
     baseline/_ref; nothing of this library on the path) on the decode or prefill workload of this file, eagerly
     and, for decode, inside a CUDA graph exactly as its runner replays it. Prints one JSON line."""
@@ -615,13 +689,14 @@ def run_reference_gpu_arm(args):
             raise RuntimeError(f"reference backend unavailable: {status.reason}")
         backend = RL.get_backend()
     except Exception as exc:
-        print(json.dumps({"impl": "reference-gpu", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}))
-        return
+        line = {"impl": "reference-gpu", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+        if emit:
+            print(json.dumps(line))
+        return line
     from nanovllm_voxcpm_b200 import batch_plan as BP
     from nanovllm_voxcpm_b200 import workloads as W
 
-    torch.cuda.set_device(0)
-    device = torch.device("cuda", 0)
+    device = torch.device("cuda", torch.cuda.current_device())
     decode = args.workload == "decode"
     if decode:
         slots, work = build_gpu_workload(device, args.layers)
@@ -691,14 +766,17 @@ def run_reference_gpu_arm(args):
     ms = s.elapsed_time(e) / args.steps
     value = bytes_step / (ms * 1e-3) / 1e9
     nproj = sum(len(layer) for layer in work) if decode else len(work[0])
-    print(json.dumps({
+    line = {
         "impl": "reference-gpu", "metric": METRIC if decode else "multi-LoRA linear GB/s (prefill SGMV, algorithmic bytes)",
         "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": config_dict(args.layers) if decode else {"workload": "prefill layer (see --workload prefill)"},
         "launch_mode": mode, "us_per_projection_call": ms * 1e3 / nproj,
         "backend": type(backend).__name__,
-    }))
+    }
+    if emit:
+        print(json.dumps(line))
+    return line
 
 
 # ------------------------------------------------------------------ whole decoder step around the LoRA linears
@@ -1033,6 +1111,276 @@ def run_tp_arm(args):
     dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------ 8-GPU class decoder (config 5) and multi-GPU blocks
+CONFIG5 = dict(hidden_size=4096, num_heads=32, num_kv_heads=8, head_dim=128, intermediate_size=14336, max_lora_rank=64)
+N_REGISTERED_5, N_DECODE_5, PREFILL_LENS_5 = 1024, 512, [1024] * 8
+
+
+def _ranks():
+    return int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def _init_dist(device):
+    """NCCL process group for the plumbing (NVLS off: in-switch reduction is not needed by this path, and the
+    exchange buffers of this library are never bound to a multicast object)."""
+    import torch.distributed as dist
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=device)
+    return dist
+
+
+def _max_over_ranks(value, device, world):
+    if world == 1:
+        return float(value)
+    import torch.distributed as dist
+
+    t = torch.tensor([float(value)], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _replica_layers(on: bool):
+    """Request-level replicas under torchrun: every rank builds the WHOLE model (the layers must not see the
+    process group as a tensor-parallel group)."""
+    from nanovllm_voxcpm_b200 import layers as L
+
+    if on:
+        L._get_world_size, L._get_rank = (lambda: 1), (lambda: 0)
+    else:
+        from nanovllm_voxcpm_b200.distributed import get_tp_rank, get_tp_world_size
+
+        L._get_world_size, L._get_rank = get_tp_world_size, get_tp_rank
+
+
+def measure_backbone_replica(device, n_layers=24, decode_steps=128):
+    """Config-4 decoder step (24 layers, hidden 1024, 64 requests, 128 resident rank-32 adapters, Zipf) on this GPU:
+    one prefill pass over all prompts, then graph-replayed decode steps. Returns tokens and device milliseconds."""
+    from nanovllm_voxcpm_b200 import backbone as BB
+    from nanovllm_voxcpm_b200 import layers as L_
+
+    cfg = BB.DecoderConfig(num_layers=n_layers)
+    gen = torch.Generator().manual_seed(0)
+    prompts = torch.randint(128, 513, (64,), generator=gen).tolist()
+    work = BB.BackboneWorkload(prompts, BB.zipf_adapters(64, cfg.max_loras, 1.1, seed=0), decode_steps)
+    with torch.device(device):
+        model = BB.Decoder(cfg).to(torch.bfloat16)
+    model.init_random_(0)
+    model.fill_adapter_slots_(cfg.max_loras, cfg.max_lora_rank, seed=1)
+    model.fused_glue = True
+    L_.LORA_FIRST = True
+    try:
+        runner = BB.BackboneRunner(model, work, use_lora=True)
+        runner.prefill()
+        p_tok, p_ms = runner.prefill()
+        d_tok, d_ms, mode = runner.decode(decode_steps, use_graph=True)
+    finally:
+        L_.LORA_FIRST = False
+    del runner, model
+    torch.cuda.empty_cache()
+    return {"prefill_tokens": p_tok, "prefill_ms": p_ms, "decode_tokens": d_tok, "decode_ms": d_ms, "launch_mode": mode,
+            "decode_steps": decode_steps}
+
+
+def backbone_replicas_block(device, world):
+    """The metric's second half: the config-4 decoder step as `world` request-level replicas (one per GPU, no
+    data-path collective): tokens of all ranks / the slowest rank's device time."""
+    _replica_layers(True)
+    try:
+        r = measure_backbone_replica(device)
+    finally:
+        _replica_layers(False)
+    p_ms = _max_over_ranks(r["prefill_ms"], device, world)
+    d_ms = _max_over_ranks(r["decode_ms"], device, world)
+    return {"parallelism": f"{world} replicas", "workload": "24-layer decoder, hidden 1024, 64 requests per replica, prompts 128-512, "
+            f"{r['decode_steps']} decode steps, 128 resident adapters rank 32, Zipf(1.1)",
+            "decode_tokens_per_s": r["decode_tokens"] * world / (d_ms * 1e-3),
+            "prefill_tokens_per_s": r["prefill_tokens"] * world / (p_ms * 1e-3),
+            "decode_ms_per_step": d_ms / r["decode_steps"], "prefill_ms": p_ms, "launch_mode": r["launch_mode"]}
+
+
+def _config5_requests(resident_slots):
+    """Adapter of each request of the step (512 decode requests + 8 prompts): ids ~ Zipf(1.1) over the 1024
+    registered adapters, admitted into the resident slots in order of first use; requests whose adapter would not
+    fit (more distinct adapters than slots) share the slot id modulo the slot count."""
+    from nanovllm_voxcpm_b200 import backbone as BB
+
+    ids = BB.zipf_adapters(N_DECODE_5 + len(PREFILL_LENS_5), N_REGISTERED_5, 1.1, seed=0)
+    slot_of, overflow = {}, 0
+    for a in ids:
+        if a not in slot_of:
+            if len(slot_of) < resident_slots:
+                slot_of[a] = len(slot_of)
+            else:
+                slot_of[a] = a % resident_slots
+                overflow += 1
+    slots = [slot_of[a] for a in ids]
+    return slots[:N_DECODE_5], slots[N_DECODE_5:], len(set(ids)), overflow
+
+
+def measure_config5(device, n_layers, slab_budget_gb, iters, use_lora=True):
+    """One mixed step (512 decode rows + an 8192-token prefill chunk) of the 8-GPU class decoder on this rank's
+    share of the model (the layers shard themselves by the tensor-parallel world they see)."""
+    from nanovllm_voxcpm_b200 import backbone as BB
+    from nanovllm_voxcpm_b200 import layers as L
+
+    tp = L._get_world_size()
+    mode = "peer_exchange" if tp > 1 else "partial_y"
+    with torch.device("meta"):
+        probe = BB.Decoder(BB.DecoderConfig(num_layers=1, max_loras=1, lora_tp_mode=mode, **CONFIG5))
+    per_slot = sum(t.numel() for m in L.iter_lora_modules(probe) for t in (*m._a_slices(), *m._b_slices())) * 2 * n_layers
+    slots = int(max(8, min(N_REGISTERED_5, slab_budget_gb * 1e9 // per_slot)))
+    cfg = BB.DecoderConfig(num_layers=n_layers, max_loras=slots, lora_tp_mode=mode, **CONFIG5)
+    with torch.device(device):
+        model = BB.Decoder(cfg).to(torch.bfloat16)
+    model.init_random_(0)
+    model.fill_adapter_slots_(slots, cfg.max_lora_rank, seed=1)
+    model.fused_glue = True
+    exchange = None
+    if tp > 1:
+        from nanovllm_voxcpm_b200.tp_exchange import TpExchange
+
+        exchange = TpExchange(capacity=(N_DECODE_5 + sum(PREFILL_LENS_5)) * cfg.max_lora_rank)
+        model.attach_tp_exchange(exchange)
+    dec, pre, distinct, overflow = _config5_requests(slots)
+    tokens, ms, _ = BB.time_mixed_step(model, N_DECODE_5, PREFILL_LENS_5, dec, pre, iters=iters, use_lora=use_lora)
+    info = {"resident_slots": slots, "slab_gb_per_gpu": per_slot * slots / 1e9, "distinct_adapters_in_step": distinct,
+            "requests_sharing_a_slot": overflow, "lora_tp_mode": mode}
+    return tokens, ms, info, model, exchange
+
+
+def run_backbone5_arm(args):
+    """BASELINE config 5: random-init 32-layer decoder, hidden 4096, 32 / 8 heads x 128, intermediate 14336, bf16;
+    1024 registered rank-64 adapters, a step of 512 decode sequences + one 8192-token prefill chunk. Under torchrun
+    the N ranks form one tensor-parallel group (`--parallelism tp`, default) or N request-level replicas
+    (`--parallelism replicas`)."""
+    from nanovllm_voxcpm_b200 import _native as N
+
+    world, rank, local = _ranks()
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        _init_dist(device)
+    replicas = world > 1 and args.parallelism == "replicas"
+    _replica_layers(replicas)
+    tp = 1 if replicas or world == 1 else world
+    iters = max(3, min(args.steps, 10))
+    tokens, ms, info, model, exchange = measure_config5(device, args.layers if args.layers != N_LAYERS else 32,
+                                                        args.slab_gb, iters)
+    base_tokens, base_ms = tokens, None
+    if not args.no_base:
+        from nanovllm_voxcpm_b200 import backbone as BB
+
+        dec, pre, _, _ = _config5_requests(info["resident_slots"])
+        _, base_ms, _ = BB.time_mixed_step(model, N_DECODE_5, PREFILL_LENS_5, dec, pre, iters=iters, use_lora=False)
+        base_ms = _max_over_ranks(base_ms, device, world)
+    ms = _max_over_ranks(ms, device, world)
+    n_rep = world if replicas else 1
+    line = {
+        "metric": "decoder backbone tokens/s, 8-GPU class model (512 decode rows + 8192-token prefill chunk per step)",
+        "value": tokens * n_rep / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": iters, "warmup": 2,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak" if replicas else "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{model.cfg.num_layers}-layer decoder, hidden 4096, 32/8 heads x 128, intermediate 14336; "
+                               f"{N_REGISTERED_5} registered adapters rank 64; step = {N_DECODE_5} decode rows + "
+                               f"{sum(PREFILL_LENS_5)}-token prefill chunk ({len(PREFILL_LENS_5)} prompts)",
+                   "parallelism": f"{world} replicas x tp1" if replicas else f"tp{tp}",
+                   "residency": "adapters are admitted into the resident slots in order of first use (LRU through SlotLoader "
+                                "in a serving loop); the step's adapters are resident before the timed region"},
+        **info, "device_status": N.device_status(),
+    }
+    if base_ms is not None:
+        line["without_adapters_ms_per_step"] = base_ms
+        line["adapter_overhead"] = ms / base_ms
+    if exchange is not None:
+        line["exchange_us"] = _exchange_times(exchange, device, model.cfg.max_lora_rank, model.cfg.hidden_size)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _exchange_times(exchange, device, r, hidden):
+    """[T, r] exchange of the row-parallel layers: the peer-memory kernel against NCCL for the decode rows (fp32), NCCL
+    for the prefill chunk (bf16), and the [T, hidden] sum of the base output that every row-parallel layer pays anyway."""
+    import torch.distributed as dist
+
+    def timed(fn, reps=50):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(reps):
+            fn()
+        e.record()
+        e.synchronize()
+        return _max_over_ranks(s.elapsed_time(e) / reps * 1e3, device, dist.get_world_size())
+
+    T = N_DECODE_5 + sum(PREFILL_LENS_5)
+    dec = torch.randn(N_DECODE_5 * r, device=device)
+    pre = torch.randn(sum(PREFILL_LENS_5), r, device=device).to(torch.bfloat16)
+    full = torch.randn(T, hidden, device=device).to(torch.bfloat16)
+    return {"decode_rows_[512,r]_fp32": {"bytes": dec.numel() * 4, "peer_kernel_us": timed(lambda: exchange.all_reduce_(dec)),
+                                         "nccl_us": timed(lambda: dist.all_reduce(dec))},
+            "prefill_rows_[8192,r]_bf16": {"bytes": pre.numel() * 2, "nccl_us": timed(lambda: dist.all_reduce(pre))},
+            "base_output_[T,hidden]_bf16": {"bytes": full.numel() * 2, "nccl_us": timed(lambda: dist.all_reduce(full), 20)}}
+
+
+def tp_block(device, world, rank):
+    """Tensor-parallel block of the N-GPU line: (1) parity of a small decoder under TP = N against the same decoder
+    on one GPU (rank 0), same seeded weights and adapters, a mixed step; (2) an 8-layer slice of the 8-GPU class
+    decoder under TP = N: tokens/s of the mixed step and the exchange times."""
+    from nanovllm_voxcpm_b200 import backbone as BB
+    from nanovllm_voxcpm_b200.tp_exchange import TpExchange
+
+    # ---- (1) parity on a small case
+    small = dict(hidden_size=512, num_heads=8, num_kv_heads=8, head_dim=64, intermediate_size=1024, num_layers=2,
+                 max_loras=4, max_lora_rank=32, max_position=1024)
+    gen = torch.Generator().manual_seed(5)
+    n_dec, lens = 16, [300, 212, 130]
+    dec = torch.randint(-1, 4, (n_dec,), generator=gen).tolist()
+    pre = [0, 3, 1]
+
+    def run_small(mode):
+        with torch.device(device):
+            m = BB.Decoder(BB.DecoderConfig(lora_tp_mode=mode, **small)).to(torch.bfloat16)
+        m.load_full_random_(4, 32, seed=9, std=0.05)
+        m.fused_glue = True
+        if mode == "peer_exchange":
+            m.attach_tp_exchange(TpExchange(capacity=(n_dec + sum(lens)) * 32))
+        return BB.time_mixed_step(m, n_dec, lens, dec, pre, context_len=40, iters=1, warmup=1)[2].float()
+
+    out_tp = run_small("peer_exchange")
+    parity = "ok"
+    if rank == 0:
+        _replica_layers(True)
+        try:
+            out_1 = run_small("partial_y")
+        finally:
+            _replica_layers(False)
+        err = float((out_tp - out_1).abs().max())
+        parity = "ok" if err <= 6e-2 and float(out_1.abs().max()) > 0.1 else f"max-abs difference {err:.3g}"
+    # ---- (2) the 8-GPU class layers under TP = N
+    tokens, ms, info, model, exchange = measure_config5(device, 8, 40.0, 3)
+    ms = _max_over_ranks(ms, device, world)
+    block = {"parallelism": f"tp{world}", "tp_parity": parity,
+             "workload": "8 layers of the 8-GPU class decoder (hidden 4096, 32/8 heads x 128, intermediate 14336), "
+                         f"{N_DECODE_5} decode rows + {sum(PREFILL_LENS_5)}-token prefill chunk per step",
+             "tokens_per_s": tokens / (ms * 1e-3), "ms_per_step": ms, **info,
+             "exchange_us": _exchange_times(exchange, device, model.cfg.max_lora_rank, model.cfg.hidden_size)}
+    del model
+    torch.cuda.empty_cache()
+    return block
+
+
+
 def main():
     args = parse_args()
     if args.workload == "tp":
@@ -1043,6 +1391,8 @@ def main():
         return run_glue_arm(args)
     if args.workload == "backbone" and args.impl in ("b200", "reference-gpu"):
         return run_backbone_arm(args)
+    if args.workload == "backbone5":
+        return run_backbone5_arm(args)
     if args.impl == "reference":
         run_reference_arm(args)
     elif args.impl == "reference-gpu":

@@ -27,7 +27,7 @@ from . import glue as G
 from . import layers as L
 from . import lora as LORA
 from .batch_plan import GraphLoRABuffers, build_lora_batch_plan_from_token_to_slot, build_lora_context_from_batch_plan
-from .context import LoRAContext, reset_lora_context, set_lora_context
+from .context import LoRAContext, build_mixed_lora_context, reset_lora_context, set_lora_context
 
 
 @dataclass
@@ -44,6 +44,9 @@ class DecoderConfig:
     max_loras: int = 128
     max_lora_rank: int = 32
     kv_block_size: int = 256
+    #: how the row-parallel layers (o, down) handle their LoRA delta under tensor parallelism
+    #: (``layers.LoRARowParallelLinear``): "partial_y" (the reference's), "allreduce_tmp", "peer_exchange"
+    lora_tp_mode: str = "partial_y"
 
 
 @dataclass
@@ -56,6 +59,9 @@ class AttentionStep:
     max_seqlen: int = 0
     context_lens: torch.Tensor | None = None   # int32 [B]    (decode, new token included)
     block_tables: torch.Tensor | None = None   # int32 [B, blocks per request]
+    #: mixed step (``is_prefill`` True and ``n_decode`` > 0): rows ``[0, n_decode)`` are single-token decode rows
+    #: (``context_lens`` / ``block_tables`` describe them), the rest is a prefill chunk (``cu_seqlens``)
+    n_decode: int = 0
 
 
 def _rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -73,52 +79,51 @@ class DecoderAttention(nn.Module):
     def __init__(self, cfg: DecoderConfig):
         super().__init__()
         self.cfg = cfg
-        self.q_size = cfg.num_heads * cfg.head_dim
-        self.kv_size = cfg.num_kv_heads * cfg.head_dim
+        tp = L._get_world_size()  # heads are split over the tensor-parallel ranks, as the layers split their weights
+        self.heads, self.kv_heads = L.divide(cfg.num_heads, tp), L.divide(cfg.num_kv_heads, tp)
+        self.q_size = self.heads * cfg.head_dim
+        self.kv_size = self.kv_heads * cfg.head_dim
         self.qkv_proj = L.LoRAQKVParallelLinear(cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.num_kv_heads,
                                                 max_loras=cfg.max_loras, max_lora_rank=cfg.max_lora_rank)
-        self.o_proj = L.LoRARowParallelLinear(self.q_size, cfg.hidden_size, max_loras=cfg.max_loras,
-                                              max_lora_rank=cfg.max_lora_rank)
+        self.o_proj = L.LoRARowParallelLinear(cfg.num_heads * cfg.head_dim, cfg.hidden_size, max_loras=cfg.max_loras,
+                                              max_lora_rank=cfg.max_lora_rank, lora_tp_mode=cfg.lora_tp_mode)
         self.k_cache = self.v_cache = None  # [blocks, block_size, kv_heads, head_dim], set by the harness
 
     def forward(self, positions, hidden, step: AttentionStep, cos_sin) -> torch.Tensor:
-        from flash_attn import flash_attn_varlen_func, flash_attn_with_kvcache
-
         cfg = self.cfg
         qkv = self.qkv_proj(hidden)
         q, k, v = qkv.split([self.q_size, self.kv_size, self.kv_size], dim=-1)
         cos, sin = cos_sin
-        q = _rope(q.view(-1, cfg.num_heads, cfg.head_dim), cos, sin)
-        k = _rope(k.view(-1, cfg.num_kv_heads, cfg.head_dim), cos, sin)
-        v = v.reshape(-1, cfg.num_kv_heads, cfg.head_dim)
-        flat_k = self.k_cache.view(-1, cfg.num_kv_heads, cfg.head_dim)
-        flat_v = self.v_cache.view(-1, cfg.num_kv_heads, cfg.head_dim)
+        q = _rope(q.view(-1, self.heads, cfg.head_dim), cos, sin)
+        k = _rope(k.view(-1, self.kv_heads, cfg.head_dim), cos, sin)
+        v = v.reshape(-1, self.kv_heads, cfg.head_dim)
+        flat_k = self.k_cache.view(-1, self.kv_heads, cfg.head_dim)
+        flat_v = self.v_cache.view(-1, self.kv_heads, cfg.head_dim)
         flat_k.index_copy_(0, step.slot_mapping, k)
         flat_v.index_copy_(0, step.slot_mapping, v)
-        scale = cfg.head_dim ** -0.5
+        return self.o_proj(self._attend(q, k, v, step).reshape(-1, self.q_size))
+
+    def _attend(self, q, k, v, step: AttentionStep) -> torch.Tensor:
+        """flash_attn over the paged cache (decode rows) and / or the packed prompts (prefill rows)."""
+        from flash_attn import flash_attn_varlen_func, flash_attn_with_kvcache
+
+        scale = self.cfg.head_dim ** -0.5
+        nd = step.n_decode if step.is_prefill else q.size(0)
+        outs = []
+        if nd:
+            outs.append(flash_attn_with_kvcache(q[:nd].unsqueeze(1), self.k_cache, self.v_cache, cache_seqlens=step.context_lens,
+                                                block_table=step.block_tables, softmax_scale=scale, causal=True).squeeze(1))
         if step.is_prefill:
-            out = flash_attn_varlen_func(q, k, v, step.cu_seqlens, step.cu_seqlens, step.max_seqlen, step.max_seqlen,
-                                         softmax_scale=scale, causal=True)
-        else:
-            out = flash_attn_with_kvcache(q.unsqueeze(1), self.k_cache, self.v_cache, cache_seqlens=step.context_lens,
-                                          block_table=step.block_tables, softmax_scale=scale, causal=True)
-        return self.o_proj(out.reshape(-1, self.q_size))
+            outs.append(flash_attn_varlen_func(q[nd:], k[nd:], v[nd:], step.cu_seqlens, step.cu_seqlens, step.max_seqlen,
+                                               step.max_seqlen, softmax_scale=scale, causal=True))
+        return outs[0] if len(outs) == 1 else torch.cat(outs, dim=0)
 
     def forward_fused(self, positions, normed, step: AttentionStep, cos, sin, slot_mapping_i32) -> torch.Tensor:
         """Same as ``forward`` with RoPE and the cache store as one in-place kernel over the packed qkv rows."""
-        from flash_attn import flash_attn_varlen_func, flash_attn_with_kvcache
-
         cfg = self.cfg
-        q, k, v = G.rope_kv_store(self.qkv_proj(normed), cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, positions=positions,
+        q, k, v = G.rope_kv_store(self.qkv_proj(normed), self.heads, self.kv_heads, cfg.head_dim, positions=positions,
                                   cos=cos, sin=sin, k_cache=self.k_cache, v_cache=self.v_cache, slot_mapping=slot_mapping_i32)
-        scale = cfg.head_dim ** -0.5
-        if step.is_prefill:
-            out = flash_attn_varlen_func(q, k, v, step.cu_seqlens, step.cu_seqlens, step.max_seqlen, step.max_seqlen,
-                                         softmax_scale=scale, causal=True)
-        else:
-            out = flash_attn_with_kvcache(q.unsqueeze(1), self.k_cache, self.v_cache, cache_seqlens=step.context_lens,
-                                          block_table=step.block_tables, softmax_scale=scale, causal=True)
-        return self.o_proj(out.reshape(-1, self.q_size))
+        return self.o_proj(self._attend(q, k, v, step).reshape(-1, self.q_size))
 
 
 class DecoderMLP(nn.Module):
@@ -127,7 +132,7 @@ class DecoderMLP(nn.Module):
         self.gate_up_proj = L.LoRAMergedColumnParallelLinear(cfg.hidden_size, [cfg.intermediate_size] * 2,
                                                              max_loras=cfg.max_loras, max_lora_rank=cfg.max_lora_rank)
         self.down_proj = L.LoRARowParallelLinear(cfg.intermediate_size, cfg.hidden_size, max_loras=cfg.max_loras,
-                                                 max_lora_rank=cfg.max_lora_rank)
+                                                 max_lora_rank=cfg.max_lora_rank, lora_tp_mode=cfg.lora_tp_mode)
 
     def forward(self, x):
         gate, up = self.gate_up_proj(x).chunk(2, dim=-1)
@@ -215,11 +220,52 @@ class Decoder(nn.Module):
                 mod.lora_scaling[:n_slots] = 1.0
                 mod.lora_base_scaling[:n_slots] = 1.0
 
+    def attach_tp_exchange(self, exchange) -> None:
+        """One ``TpExchange`` shared by the row-parallel layers (``lora_tp_mode="peer_exchange"``)."""
+        for layer in self.layers:
+            layer.self_attn.o_proj.tp_exchange = exchange
+            layer.mlp.down_proj.tp_exchange = exchange
+
+    def load_full_random_(self, n_slots: int, rank: int, seed: int = 0, std: float = 0.02) -> None:
+        """Full (unsharded) random base weights and adapters drawn from one seeded generator, the same on every
+        rank, loaded through the layers' own shard loaders: a tensor-parallel model and a single-GPU model built
+        with the same seed then compute the same function. Meant for small parity cases (every rank materialises
+        the full tensors)."""
+        dev = self.norm.device
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        dt = self.layers[0].self_attn.qkv_proj.weight.dtype
+        rn = lambda *shape: (torch.randn(*shape, generator=gen, device=dev) * std).to(dt)  # noqa: E731
+        cfg = self.cfg
+        hq, hkv = cfg.num_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+        with torch.no_grad():
+            for layer in self.layers:
+                qkv, o, gu, down = layer.self_attn.qkv_proj, layer.self_attn.o_proj, layer.mlp.gate_up_proj, layer.mlp.down_proj
+                for shard, rows in (("q", hq), ("k", hkv), ("v", hkv)):
+                    qkv.load_base_shard(rn(rows, cfg.hidden_size), shard)
+                o.load_base_shard(rn(cfg.hidden_size, hq))
+                for i in range(2):
+                    gu.load_base_shard(rn(cfg.intermediate_size, cfg.hidden_size), i)
+                down.load_base_shard(rn(cfg.hidden_size, cfg.intermediate_size))
+                tp, r = qkv.tp_size, qkv.tp_rank
+                for slot in range(n_slots):
+                    a = rn(3, rank, cfg.hidden_size)
+                    b = [rn(rows, rank).chunk(tp, 0)[r] for rows in (hq, hkv, hkv)]
+                    qkv.set_slot_lora(slot, a, b, rank, 1.0)
+                    a = rn(2, rank, cfg.hidden_size)
+                    b = [rn(cfg.intermediate_size, rank).chunk(tp, 0)[r] for _ in range(2)]
+                    gu.set_slot_lora(slot, a, b, rank, 1.0)
+                    for mod, width in ((o, hq), (down, cfg.intermediate_size)):
+                        a, b = rn(rank, width).chunk(tp, 1)[r], rn(cfg.hidden_size, rank)
+                        if mod.lora_tp_mode != "partial_y":
+                            b = b.chunk(tp, 0)[r]
+                        mod.set_slot_lora(slot, a.contiguous(), b.contiguous(), rank, 1.0)
+
     def allocate_kv_cache(self, num_blocks: int) -> None:
         cfg = self.cfg
         dev, dt = self.norm.device, self.layers[0].self_attn.qkv_proj.weight.dtype
+        kv_heads = self.layers[0].self_attn.kv_heads
         for layer in self.layers:
-            layer.self_attn.k_cache = torch.zeros(num_blocks, cfg.kv_block_size, cfg.num_kv_heads, cfg.head_dim, device=dev, dtype=dt)
+            layer.self_attn.k_cache = torch.zeros(num_blocks, cfg.kv_block_size, kv_heads, cfg.head_dim, device=dev, dtype=dt)
             layer.self_attn.v_cache = torch.zeros_like(layer.self_attn.k_cache)
 
 
@@ -349,3 +395,52 @@ class BackboneRunner:
         reset_lora_context()
         self.last_output = out
         return B * steps, start.elapsed_time(end), mode
+
+
+@torch.inference_mode()
+def time_mixed_step(model: Decoder, n_decode: int, prefill_lens: list[int], slots_decode: list[int], slots_prefill: list[int],
+                    context_len: int = 200, iters: int = 5, warmup: int = 2, use_lora: bool = True, seed: int = 3):
+    """One continuous-batching step that holds ``n_decode`` single-token decode rows (requests with ``context_len``
+    tokens in the paged cache) AND a prefill chunk of whole prompts (``prefill_lens``), as a scheduler that mixes
+    the two kinds builds it: rows ``[0, n_decode)`` decode, then the prompts packed. Attention runs per kind
+    (paged decode / varlen prefill); every LoRA layer issues one multi-LoRA call per kind
+    (``LoRAContext.parts``). Returns (tokens per step, milliseconds per step on the device, last output)."""
+    cfg, dev = model.cfg, model.norm.device
+    dtype = model.layers[0].self_attn.qkv_proj.weight.dtype
+    bs = cfg.kv_block_size
+    per_decode = -(-(context_len + 1) // bs)
+    blocks_prefill = [-(-n // bs) for n in prefill_lens]
+    model.allocate_kv_cache(n_decode * per_decode + sum(blocks_prefill))
+    block_tables = torch.arange(n_decode * per_decode, dtype=torch.int32, device=dev).view(n_decode, per_decode)
+    T_pre = sum(prefill_lens)
+    # cache position of every new token
+    dec_pos = block_tables[:, context_len // bs].long() * bs + context_len % bs
+    first = n_decode * per_decode
+    pre_pos, positions = [], [torch.full((n_decode,), context_len, dtype=torch.int64)]
+    for n, nb in zip(prefill_lens, blocks_prefill):
+        pre_pos.append(first * bs + torch.arange(n))
+        positions.append(torch.arange(n))
+        first += nb
+    slot_mapping = torch.cat([dec_pos.cpu(), *pre_pos]).to(dev)
+    positions = torch.cat(positions).to(dev)
+    cu = torch.tensor([0] + list(torch.tensor(prefill_lens).cumsum(0)), dtype=torch.int32, device=dev)
+    step = AttentionStep(True, slot_mapping, cu_seqlens=cu, max_seqlen=max(prefill_lens),
+                         context_lens=torch.full((n_decode,), context_len + 1, dtype=torch.int32, device=dev),
+                         block_tables=block_tables, n_decode=n_decode)
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    embeds = torch.randn(n_decode + T_pre, cfg.hidden_size, device=dev, generator=gen).to(dtype)
+    tts = torch.cat([torch.tensor(slots_decode, dtype=torch.int32),
+                     torch.repeat_interleave(torch.tensor(slots_prefill, dtype=torch.int32), torch.tensor(prefill_lens))])
+    ctx = build_mixed_lora_context(tts.to(dev), [n_decode]) if use_lora else None
+    out = None
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(warmup + iters):
+        if i == warmup:
+            torch.cuda.synchronize()
+            start.record()
+        set_lora_context(ctx) if ctx is not None else reset_lora_context()
+        out = model(embeds, positions, step)
+    end.record()
+    end.synchronize()
+    reset_lora_context()
+    return n_decode + T_pre, start.elapsed_time(end) / iters, out

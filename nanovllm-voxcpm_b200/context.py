@@ -24,6 +24,12 @@ class LoRAContext:
     slot_start_offsets: torch.Tensor | None = None
     no_lora_flag: bool = True
     num_active_loras: int = 0
+    #: Row ranges of a step that mixes batch kinds, e.g. single-token decode rows next to a prefill chunk:
+    #: ``[(first_row, end_row, LoRAContext of those rows), ...]``. The layers then issue one multi-LoRA call per
+    #: range (the decode kernel for the scattered rows, the tensor-core kernels for the request-contiguous ones)
+    #: instead of one call that suits neither. The reference's scheduler never mixes the two kinds
+    #: (``nanovllm_voxcpm/engine/scheduler.py:108-140``), so its contexts have no such field.
+    parts: list | None = None
     # LoRAMetadata view shared by all layers of the domain within one step
     _cached_metadata: object | None = field(default=None, repr=False, compare=False)
 
@@ -71,6 +77,21 @@ def build_lora_context_from_token_to_slot(token_to_slot: torch.Tensor | None) ->
         no_lora_flag=False,
         num_active_loras=int(active.numel()),
     )
+
+
+def build_mixed_lora_context(token_to_slot: torch.Tensor, split_rows: list[int]) -> LoRAContext:
+    """Context of a step whose rows ``[0, split_rows[0])``, ``[split_rows[0], split_rows[1])``, ... are batches of
+    different kinds (decode rows first, then prefill chunks): every range gets its own eager-plan metadata."""
+    tts = token_to_slot.to(dtype=torch.int32)
+    bounds = [0, *[int(r) for r in split_rows], int(tts.numel())]
+    parts = []
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        if hi > lo:
+            parts.append((lo, hi, build_lora_context_from_token_to_slot(tts[lo:hi])))
+    whole = LoRAContext(token_to_slot=tts, no_lora_flag=all(p[2].no_lora_flag for p in parts),
+                        num_active_loras=max([p[2].num_active_loras for p in parts], default=0))
+    whole.parts = parts
+    return whole
 
 
 def set_lora_context_from_token_to_slot(token_to_slot: torch.Tensor | None, *, domain: str = LM_LORA_DOMAIN) -> None:

@@ -442,6 +442,20 @@ int lora_b200_shrink(void* out, int32_t out_dtype, const void* x, int64_t x_ld, 
   SliceTable st;
   if (int rc = fill_slices(st, n_slices, a_slabs, nullptr, nullptr, nullptr, true, false)) return rc;
   cudaStream_t st_ = static_cast<cudaStream_t>(stream);
+  if (dtype == B200_LORA_BF16 && out_dtype == B200_LORA_BF16 && T >= kSgmvAutoMinTokens) {
+    // prefill-sized bf16 batches: the tensor-core shrink (rows without adapter are written as zeros, as the
+    // per-token kernel does); anything it does not take falls through to the per-token kernel
+    SgmvProblem sp;
+    sp.y = nullptr; sp.y_ld = 0; sp.x = x; sp.x_ld = x_ld; sp.T = T; sp.in_dim = in_dim; sp.S = S; sp.r_max = r_max;
+    sp.st = st; sp.scale_per_slot = nullptr; sp.token_to_slot = token_to_slot; sp.scaling = scaling;
+    if (sgmv_supported(sp, nullptr, true, false) && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
+      SgmvMaps sm;
+      SgmvArgs sa;
+      if (int rc = sgmv_prepare_tmp(sp, out, (uint64_t)st.n * T, true, false, &sm, &sa)) return rc;
+      sa.zero_fill = 1;
+      return sgmv_launch_shrink(sm, sa, st_);
+    }
+  }
 #define B200_SHRINK(TT)                                                                              \
   (out_dtype == B200_LORA_F32 && dtype != B200_LORA_F32)                                             \
       ? launch_generic_shrink<TT, float>(out, x, x_ld, T, in_dim, st, S, r_max, token_to_slot, scaling, st_) \
@@ -470,6 +484,35 @@ int lora_b200_expand(void* y, int64_t y_ld, const void* tmp, int32_t tmp_dtype, 
   for (int s = 0; s < st.n; ++s)
     if (y_ld < (int64_t)st.col[s] + st.out[s]) return fail(B200_LORA_EINVAL, "y_ld smaller than slice end");
   cudaStream_t st_ = static_cast<cudaStream_t>(stream);
+  if (dtype == B200_LORA_BF16 && tmp_dtype == B200_LORA_BF16 && add_inputs && T >= kSgmvAutoMinTokens) {
+    // prefill-sized bf16 batches: the tensor-core expand (reduce-add tile kernel when the slices tile the
+    // columns they cover in 64-column units, run-based kernel otherwise)
+    int first = -1;
+    for (int s = 0; s < st.n; ++s)
+      if (st.out[s] > 0 && (first < 0 || st.col[s] < first)) first = st.col[s];
+    bool dense = first >= 0;  // no zero-width slice in between: tmp is indexed by slice position
+    for (int s = 0; s < st.n; ++s) dense = dense && st.out[s] > 0;
+    if (dense && first % 8 == 0) {
+      SgmvProblem sp;
+      sp.y = static_cast<char*>(y) + (size_t)first * 2; sp.y_ld = y_ld; sp.x = nullptr; sp.x_ld = 0; sp.T = T; sp.in_dim = 0;
+      sp.S = S; sp.r_max = r_max; sp.st = st; sp.scale_per_slot = nullptr; sp.token_to_slot = token_to_slot; sp.scaling = 1.0f;
+      for (int s = 0; s < st.n; ++s) sp.st.col[s] -= first;
+      if (sgmv_supported(sp, nullptr, false, true) && (reinterpret_cast<uintptr_t>(tmp) & 15u) == 0) {
+        SgmvMaps sm;
+        SgmvArgs sa;
+        if (int rc = sgmv_prepare_tmp(sp, const_cast<void*>(tmp), (uint64_t)st.n * T, false, true, &sm, &sa)) return rc;
+        if (tc_expand_fast_path_ok(sa)) {
+          int n_total = 0;
+          for (int s = 0; s < sa.n; ++s) n_total = std::max(n_total, sa.col[s] + sa.out[s]);
+          GemmMaps gm;
+          GemmArgs ga;
+          if (int rc = tc_tile_prepare(sm, sa, nullptr, 0, n_total, nullptr, true, true, &gm, &ga, false, false)) return rc;
+          return tc_tile_launch(gm, ga, st_);
+        }
+        return sgmv_launch_expand(sm, sa, st_);
+      }
+    }
+  }
 #define B200_EXPAND(TT)                                                                               \
   (tmp_dtype == B200_LORA_F32 && dtype != B200_LORA_F32)                                              \
       ? launch_generic_expand<TT, float>(y, y_ld, tmp, T, st, S, r_max, token_to_slot, add_inputs, st_) \

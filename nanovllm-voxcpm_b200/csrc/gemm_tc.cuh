@@ -432,7 +432,7 @@ inline bool tc_lora_stage_ok(const SgmvArgs& a) {
 // `weight` [n_total, in] row-major with pitch w_ld (LINEAR) or null (EXPAND).
 inline int tc_tile_prepare(const SgmvMaps& sm, const SgmvArgs& sa, const void* weight, int64_t w_ld, int n_total,
                            const void* bias, bool expand_mode, bool lora, GemmMaps* maps, GemmArgs* args,
-                           bool overwrite = false) {
+                           bool overwrite = false, bool after_shrink = true) {
   GemmArgs a = {};
   a.T = sa.T; a.in_dim = expand_mode ? 0 : sa.in_dim; a.n_total = n_total;
   a.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -442,7 +442,7 @@ inline int tc_tile_prepare(const SgmvMaps& sm, const SgmvArgs& sa, const void* w
   a.expand_mode = expand_mode ? 1 : 0;
   a.lora = lora ? 1 : 0;
   a.overwrite = overwrite ? 1 : 0;
-  a.after_shrink = lora ? 1 : 0;  // every caller that asks for the LoRA stages has just launched the shrink
+  a.after_shrink = (lora && after_shrink) ? 1 : 0;  // the caller has just launched the shrink that writes tmp (else: unknown predecessor)
   maps->x = sm.x; maps->t = sm.t;
   for (int s = 0; s < B200_LORA_MAX_SLICES; ++s) maps->b[s] = sm.b[s];
   maps->w = sm.x;

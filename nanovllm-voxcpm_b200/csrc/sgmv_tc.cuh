@@ -410,7 +410,8 @@ inline size_t sgmv_workspace_bytes(int T, int n_slices, int r_max) {
   return ((size_t)n_slices * (size_t)T + kSgmvBM) * (size_t)r_max * 2 + 1024;
 }
 
-inline bool sgmv_supported(const SgmvProblem& b, const char** why) {
+// `with_x` / `with_b`: which of the two halves the caller runs (shrink reads x and lora_A, expand reads tmp and lora_B)
+inline bool sgmv_supported(const SgmvProblem& b, const char** why, bool with_x = true, bool with_b = true) {
   const char* dummy;
   if (why == nullptr) why = &dummy;
   int n = 0;
@@ -418,21 +419,29 @@ inline bool sgmv_supported(const SgmvProblem& b, const char** why) {
   if (n == 0) { *why = "no active slice"; return false; }
   if (b.r_max != 16 && b.r_max != 32 && b.r_max != 64) { *why = "r_max must be 16, 32 or 64"; return false; }
   if (n * b.r_max > 512) { *why = "n_slices * r_max exceeds the 512 TMEM columns"; return false; }
-  if (b.in_dim % kSgmvBK != 0) { *why = "in_dim must be a multiple of 64"; return false; }
-  if (b.x_ld % 8 != 0 || b.y_ld % 8 != 0) { *why = "row strides must be multiples of 8 elements"; return false; }
-  if ((reinterpret_cast<uintptr_t>(b.x) & 15u) || (reinterpret_cast<uintptr_t>(b.y) & 15u)) { *why = "x / y must be 16-byte aligned"; return false; }
+  if (with_x) {
+    if (b.in_dim % kSgmvBK != 0) { *why = "in_dim must be a multiple of 64"; return false; }
+    if (b.x_ld % 8 != 0 || (reinterpret_cast<uintptr_t>(b.x) & 15u)) { *why = "x must be 16-byte aligned with a row stride that is a multiple of 8"; return false; }
+  }
+  if (with_b && (b.y_ld % 8 != 0 || (reinterpret_cast<uintptr_t>(b.y) & 15u))) { *why = "y must be 16-byte aligned with a row stride that is a multiple of 8"; return false; }
   for (int s = 0; s < b.st.n; ++s) {
     if (b.st.out[s] == 0) continue;
-    if (b.st.out[s] % 8 != 0 || b.st.col[s] % 8 != 0) { *why = "slice widths / offsets must be multiples of 8"; return false; }
-    if ((reinterpret_cast<uintptr_t>(b.st.a[s]) & 15u) || (reinterpret_cast<uintptr_t>(b.st.b[s]) & 15u)) { *why = "slabs must be 16-byte aligned"; return false; }
+    if (with_b && (b.st.out[s] % 8 != 0 || b.st.col[s] % 8 != 0)) { *why = "slice widths / offsets must be multiples of 8"; return false; }
+    if ((with_x && (reinterpret_cast<uintptr_t>(b.st.a[s]) & 15u)) || (with_b && (reinterpret_cast<uintptr_t>(b.st.b[s]) & 15u))) {
+      *why = "slabs must be 16-byte aligned";
+      return false;
+    }
   }
   return true;
 }
 
-// Builds the launch arguments and tensor maps shared by the two kernels.
-inline int sgmv_prepare(const SgmvProblem& b, void* workspace, size_t workspace_bytes, SgmvMaps* maps, SgmvArgs* args) {
+// Launch arguments and tensor maps over an intermediate `tmp` [n, T, r_max] (bf16, 16-byte aligned) that holds
+// `tmp_rows` rows: rows beyond that are neither written nor read (the maps clip).
+inline int sgmv_prepare_tmp(const SgmvProblem& b, void* tmp, uint64_t tmp_rows, bool with_x, bool with_b, SgmvMaps* maps,
+                            SgmvArgs* args) {
   const char* why = nullptr;
-  if (!sgmv_supported(b, &why)) return fail(B200_LORA_EUNSUPPORTED, "prefill kernels: %s", why);
+  if (!sgmv_supported(b, &why, with_x, with_b)) return fail(B200_LORA_EUNSUPPORTED, "prefill kernels: %s", why);
+  if (tmp == nullptr || (reinterpret_cast<uintptr_t>(tmp) & 15u)) return fail(B200_LORA_EINVAL, "prefill kernels: the intermediate must be 16-byte aligned");
   SgmvArgs a = {};
   a.n = 0;
   const void* slab_a[B200_LORA_MAX_SLICES];
@@ -443,25 +452,44 @@ inline int sgmv_prepare(const SgmvProblem& b, void* workspace, size_t workspace_
     a.out[a.n] = b.st.out[s]; a.col[a.n] = b.st.col[s];
     ++a.n;
   }
-  const size_t need = sgmv_workspace_bytes(b.T, a.n, b.r_max);
-  if (workspace == nullptr || workspace_bytes < need)
-    return fail(B200_LORA_EWORKSPACE, "prefill kernels need %zu bytes of scratch, got %zu", need, workspace_bytes);
-  uintptr_t ws = (reinterpret_cast<uintptr_t>(workspace) + 1023) & ~(uintptr_t)1023;
   a.y = static_cast<__nv_bfloat16*>(b.y); a.y_ld = b.y_ld;
-  a.tmp = reinterpret_cast<__nv_bfloat16*>(ws);
+  a.tmp = static_cast<__nv_bfloat16*>(tmp);
   a.T = b.T; a.in_dim = b.in_dim; a.S = b.S; a.r_max = b.r_max;
   a.token_to_slot = b.token_to_slot; a.scale_per_slot = b.scale_per_slot; a.scaling = b.scaling;
   a.zero_fill = 0;
-  if (int rc = make_tmap_2d(&maps->x, b.x, (uint64_t)b.T, (uint64_t)b.in_dim, (uint64_t)b.x_ld, kSgmvBM, kSgmvBK)) return rc;
-  if (int rc = make_tmap_2d(&maps->xs, b.x, (uint64_t)b.T, (uint64_t)b.in_dim, (uint64_t)b.x_ld, kShrinkRows, kSgmvBK)) return rc;
-  if (int rc = make_tmap_2d(&maps->t, a.tmp, (uint64_t)a.n * b.T + kSgmvBM, (uint64_t)b.r_max, (uint64_t)b.r_max, kSgmvBM, (uint32_t)b.r_max)) return rc;
+  if (int rc = make_tmap_2d(&maps->t, a.tmp, tmp_rows, (uint64_t)b.r_max, (uint64_t)b.r_max, kSgmvBM, (uint32_t)b.r_max)) return rc;
+  if (with_x) {
+    if (int rc = make_tmap_2d(&maps->x, b.x, (uint64_t)b.T, (uint64_t)b.in_dim, (uint64_t)b.x_ld, kSgmvBM, kSgmvBK)) return rc;
+    if (int rc = make_tmap_2d(&maps->xs, b.x, (uint64_t)b.T, (uint64_t)b.in_dim, (uint64_t)b.x_ld, kShrinkRows, kSgmvBK)) return rc;
+  } else {
+    maps->x = maps->xs = maps->t;  // never dereferenced by the expand half
+  }
   for (int s = 0; s < a.n; ++s) {
-    if (int rc = make_tmap_2d(&maps->a[s], slab_a[s], (uint64_t)b.S * b.r_max, (uint64_t)b.in_dim, (uint64_t)b.in_dim, (uint32_t)b.r_max, kSgmvBK)) return rc;
-    if (int rc = make_tmap_2d(&maps->b[s], slab_b[s], (uint64_t)b.S * a.out[s], (uint64_t)b.r_max, (uint64_t)b.r_max, kSgmvBN, (uint32_t)b.r_max)) return rc;
+    if (with_x) {
+      if (int rc = make_tmap_2d(&maps->a[s], slab_a[s], (uint64_t)b.S * b.r_max, (uint64_t)b.in_dim, (uint64_t)b.in_dim, (uint32_t)b.r_max, kSgmvBK)) return rc;
+    } else {
+      maps->a[s] = maps->t;
+    }
+    if (with_b) {
+      if (int rc = make_tmap_2d(&maps->b[s], slab_b[s], (uint64_t)b.S * a.out[s], (uint64_t)b.r_max, (uint64_t)b.r_max, kSgmvBN, (uint32_t)b.r_max)) return rc;
+    } else {
+      maps->b[s] = maps->t;
+    }
   }
   for (int s = a.n; s < B200_LORA_MAX_SLICES; ++s) { maps->a[s] = maps->a[0]; maps->b[s] = maps->b[0]; }
   *args = a;
   return B200_LORA_OK;
+}
+
+// Builds the launch arguments and tensor maps shared by the two kernels, the intermediate in caller-provided scratch.
+inline int sgmv_prepare(const SgmvProblem& b, void* workspace, size_t workspace_bytes, SgmvMaps* maps, SgmvArgs* args) {
+  int n = 0;
+  for (int s = 0; s < b.st.n; ++s) n += b.st.out[s] > 0;
+  const size_t need = sgmv_workspace_bytes(b.T, std::max(n, 1), b.r_max);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(B200_LORA_EWORKSPACE, "prefill kernels need %zu bytes of scratch, got %zu", need, workspace_bytes);
+  uintptr_t ws = (reinterpret_cast<uintptr_t>(workspace) + 1023) & ~(uintptr_t)1023;
+  return sgmv_prepare_tmp(b, reinterpret_cast<void*>(ws), (uint64_t)n * b.T + kSgmvBM, true, true, maps, args);
 }
 
 inline int sgmv_set_smem(const void* kernel, size_t bytes) {

@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <unordered_map>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -110,8 +112,40 @@ inline EncodeTiledFn encode_tiled_fn() {
 
 // 2-D bf16 row-major matrix [rows, cols] with row pitch `ld` elements; box = box_rows x box_cols,
 // swizzle chosen by the box width in bytes (128 / 64 / 32). Returns 0 or an error code.
+// A tensor map depends only on (address, shape, row stride, box), never on the data: encoded maps are kept per
+// host thread and reused, which takes the driver call (about a microsecond each, eight per prefill launch) off
+// the host side of a launch. The table is dropped when it reaches kTmapCacheEntries entries.
+struct TmapKey {
+  const void* base; uint64_t rows, cols, ld; uint32_t box_rows, box_cols;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && box_cols == o.box_cols;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.rows + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (k.cols * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2));
+    h ^= (k.ld * 0x165667B19E3779F9ull + (h << 6) + (h >> 2));
+    h ^= (((uint64_t)k.box_rows << 32 | k.box_cols) + (h << 6) + (h >> 2));
+    return (size_t)h;
+  }
+};
+constexpr size_t kTmapCacheEntries = 8192;
+inline std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash>& tmap_cache() {
+  static thread_local std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  return cache;
+}
+
 inline int make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                         uint32_t box_rows, uint32_t box_cols) {
+  const TmapKey key = {base, rows, cols, ld, box_rows, box_cols};
+  auto& cache = tmap_cache();
+  auto hit = cache.find(key);
+  if (hit != cache.end()) {
+    *out = hit->second;
+    return B200_LORA_OK;
+  }
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return fail(B200_LORA_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const uint32_t box_bytes = box_cols * 2;
@@ -128,6 +162,8 @@ inline int make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint6
                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(B200_LORA_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  if (cache.size() >= kTmapCacheEntries) cache.clear();
+  cache.emplace(key, *out);
   return B200_LORA_OK;
 }
 

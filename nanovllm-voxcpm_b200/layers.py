@@ -27,7 +27,7 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .context import LM_LORA_DOMAIN, get_lora_context
+from .context import LM_LORA_DOMAIN, get_lora_context, set_lora_context
 from .distributed import get_tp_rank, get_tp_world_size
 from .lora import B200LoRABackend, LoRAMetadata, get_backend
 
@@ -138,7 +138,8 @@ class _LoRALayerBase(nn.Module):
         ``FUSED_LINEAR`` switched on, bf16 batches of at least ``lora.SGMV_MIN_TOKENS`` rows
         take ``lora_b200_linear_lora`` instead: one tensor-core kernel whose accumulator
         receives the delta before the single store of ``y``."""
-        if FUSED_LINEAR and x.is_cuda and isinstance(get_backend(), B200LoRABackend):
+        mixed = bool(get_lora_context(self.lora_domain).parts)
+        if FUSED_LINEAR and not mixed and x.is_cuda and isinstance(get_backend(), B200LoRABackend):
             from .lora import SGMV_MIN_TOKENS, fused_linear_supported, linear_lora
 
             x_flat = x if x.dim() == 2 else x.reshape(-1, x.size(-1))
@@ -153,7 +154,7 @@ class _LoRALayerBase(nn.Module):
                         [widths[i] for i in active], [cols[i] for i in active], token_to_slot, 1.0,
                     )
                     return y if x.dim() == 2 else y.view(*x.shape[:-1], y.size(-1))
-        if LORA_FIRST and bias is None and x.is_cuda and isinstance(get_backend(), B200LoRABackend):
+        if LORA_FIRST and not mixed and bias is None and x.is_cuda and isinstance(get_backend(), B200LoRABackend):
             from .lora import launch_add
 
             x_flat = x if x.dim() == 2 else x.reshape(-1, x.size(-1))
@@ -176,8 +177,30 @@ class _LoRALayerBase(nn.Module):
                     return y if x.dim() == 2 else y.view(*x.shape[:-1], y.size(-1))
         return self._apply_lora(F.linear(x, weight, bias), x)
 
+    def _per_part(self, fn, y: torch.Tensor, x: torch.Tensor) -> torch.Tensor | None:
+        """A step that mixes batch kinds (``LoRAContext.parts``): ``fn(y_rows, x_rows)`` once per row range, each
+        under that range's own context. Returns None when the step is not mixed."""
+        whole = get_lora_context(self.lora_domain)
+        if not whole.parts:
+            return None
+        x_flat = x if x.dim() == 2 else x.reshape(-1, x.size(-1))
+        y_flat = y if y.dim() == 2 else y.view(-1, y.size(-1))
+        cached = whole._cached_metadata
+        try:
+            for lo, hi, part in whole.parts:
+                meta = part._cached_metadata  # survives the re-publication below: one metadata view per part and step
+                set_lora_context(part, domain=self.lora_domain)
+                part._cached_metadata = meta
+                fn(y_flat[lo:hi], x_flat[lo:hi])
+        finally:
+            set_lora_context(whole, domain=self.lora_domain)
+            whole._cached_metadata = cached
+        return y
+
     def _apply_lora(self, y: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
         """Add the LoRA delta of this module to ``y`` in place (fused shrink+expand)."""
+        if self._per_part(self._apply_lora, y, x) is not None:
+            return y
         x_flat = x if x.dim() == 2 else x.reshape(-1, x.size(-1))
         token_to_slot = self._resolve_token_slots(x_flat)
         if token_to_slot is None:
@@ -510,14 +533,24 @@ class LoRARowParallelLinear(_LoRALayerBase):
         self.weight.data.copy_(loaded_weight.narrow(1, self.tp_rank * self.shard_input_size, self.shard_input_size))
 
     def _apply_lora_allreduce_tmp(self, y: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        from .lora import SGMV_MIN_TOKENS
         from .lora_ops import expand_into, shrink_into
 
+        if self._per_part(self._apply_lora_allreduce_tmp, y, x) is not None:
+            return y
         x_flat = x if x.dim() == 2 else x.reshape(-1, x.size(-1))
         token_to_slot = self._resolve_token_slots(x_flat)
         if token_to_slot is None:
             return y
         y_flat = y if y.dim() == 2 else y.view(-1, y.size(-1))
-        if self.lora_tp_mode == "peer_exchange" and x.is_cuda:
+        # prefill-sized bf16 batches: both halves on the tensor-core kernels around a bf16 [T, r] sum
+        # (rows of one adapter must be contiguous for those: a batch with fewer than 32 rows per adapter bucket is a
+        # decode batch, whatever its size, and stays on the bucket kernel)
+        meta = self._runtime_metadata()
+        scattered = meta is not None and meta.num_active_loras > 0 and x_flat.size(0) < 32 * meta.num_active_loras
+        tensor_core = (x.is_cuda and x.dtype == torch.bfloat16 and x_flat.size(0) >= SGMV_MIN_TOKENS and not scattered
+                       and self.max_lora_rank in (16, 32, 64) and x_flat.size(1) % 64 == 0)
+        if self.lora_tp_mode == "peer_exchange" and x.is_cuda and not tensor_core:
             # one C call: bucket kernel (shrink half) -> peer-memory exchange -> bucket kernel (expand half)
             if self.tp_exchange is None:
                 raise RuntimeError("lora_tp_mode='peer_exchange' needs a TpExchange in layer.tp_exchange")
@@ -528,9 +561,10 @@ class LoRARowParallelLinear(_LoRALayerBase):
             self.tp_exchange.row_parallel_add(y_flat, x_flat, [self.lora_A], [self.lora_B], widths, cols, metadata, 1.0,
                                               rank_per_slot=self.effective_lora_rank)
             return y
-        tmp = torch.empty((1, x_flat.size(0), self.max_lora_rank), dtype=torch.float32, device=x.device)
+        tmp = torch.empty((1, x_flat.size(0), self.max_lora_rank), dtype=torch.bfloat16 if tensor_core else torch.float32,
+                          device=x.device)
         shrink_into(tmp, x_flat, [self.lora_A], token_to_slot, 1.0)
-        if self.lora_tp_mode == "peer_exchange":
+        if self.lora_tp_mode == "peer_exchange" and not tensor_core:
             if self.tp_exchange is None:
                 raise RuntimeError("lora_tp_mode='peer_exchange' needs a TpExchange in layer.tp_exchange")
             self.tp_exchange.all_reduce_(tmp)  # one kernel over peer memory

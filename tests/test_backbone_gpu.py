@@ -68,6 +68,33 @@ def test_backbone_prefill_and_decode_match_the_oracle_backend():
     assert torch.equal(out_prefill[217:481], out_base[217:481])
 
 
+def test_mixed_step_splits_decode_rows_and_prefill_chunk():
+    """A step that holds single-token decode rows AND a prefill chunk: every LoRA layer issues one call per row
+    range (``LoRAContext.parts``), attention runs per kind. Against the same step with the oracle formula as the
+    LoRA backend (which sees each range under its own context too), and against the step without adapters on the
+    rows that have none."""
+    model, _ = _model_and_work()
+    n_dec, lens = 24, [300, 230, 70]  # 600 prefill rows: tensor-core kernels; 24 decode rows: fused decode kernel
+    gen = torch.Generator().manual_seed(4)
+    dec = torch.randint(-1, 8, (n_dec,), generator=gen).tolist()
+    pre = [2, -1, 5]
+    for fused in (False, True):
+        model.fused_glue = fused
+        try:
+            tokens, _, out = BB.time_mixed_step(model, n_dec, lens, dec, pre, context_len=40, iters=1, warmup=1)
+            _, _, base = BB.time_mixed_step(model, n_dec, lens, dec, pre, context_len=40, iters=1, warmup=1, use_lora=False)
+            LORA.set_backend_for_testing(OracleBackend())
+            _, _, ref = BB.time_mixed_step(model, n_dec, lens, dec, pre, context_len=40, iters=1, warmup=1)
+        finally:
+            LORA.set_backend_for_testing(None)
+            model.fused_glue = False
+        assert tokens == n_dec + sum(lens)
+        torch.testing.assert_close(out.float(), ref.float(), atol=6e-2, rtol=6e-2)
+        rows = torch.tensor([i for i, s in enumerate(dec) if s < 0] + list(range(n_dec + 300, n_dec + 530)), device="cuda")
+        assert torch.equal(out[rows], base[rows]), "rows without adapter differ from the model without adapters"
+        assert not torch.allclose(out.float(), base.float(), atol=1e-3)
+
+
 def test_fused_glue_step_matches_the_torch_glue_step():
     """The same decoder with residual add + RMSNorm, RoPE + cache store and SiLU * up as single launches: outputs
     within the rounding of a two-layer bf16 stack, KV caches equal, graph replay equal to eager launches."""

@@ -234,6 +234,41 @@ def test_shrink_and_expand_ops_match_oracle():
     assert not y2.cpu()[:, :64].any()
 
 
+@pytest.mark.parametrize("name", ["qkv", "o", "gate_up", "down"])
+def test_shrink_and_expand_ops_full_size_prefill(name):
+    """``lora_shrink`` / ``lora_expand`` on the prefill configuration at full size (bf16 intermediate, 8172 rows):
+    these sizes take the tensor-core kernels; compared with the oracle's two halves, rows without adapter zero
+    in the intermediate and bit-exact in the output."""
+    p = W.prefill_projection(name, seed=0)
+    p.token_to_slot[700:777] = -1
+    d = p.to_device(DEV)
+    n, T, r = len(p.a_slabs), p.x.shape[0], p.a_slabs[0].shape[1]
+    meta = (d.token_to_slot, None, None, None, None, False, 0)
+    tmp = torch.full((n, T, r), 7.0, device=DEV, dtype=torch.bfloat16)
+    lora_shrink(d.x, d.a_slabs, tmp, *meta, 0.5)
+    torch.cuda.synchronize()
+    ref_tmp = O.shrink(p.x, p.a_slabs, p.token_to_slot, 0.5)
+    assert_lora_close(tmp, ref_tmp, what=f"shrink / {name}")
+    none = p.token_to_slot < 0
+    assert not tmp.cpu()[:, none].any(), "rows without adapter are not zero in the intermediate"
+    # expand from the oracle's intermediate rounded to bf16 (so that only the expand is under test); the last
+    # slices at a column offset, as a tensor-parallel shard's call has them
+    tmp_in = ref_tmp.to(torch.bfloat16)
+    want = O.expand(p.y, tmp_in.float(), p.b_slabs, p.token_to_slot)
+    y = d.y.clone()
+    lora_expand(tmp_in.to(DEV), d.b_slabs, y, *meta, offset_start=0, add_inputs=True)
+    torch.cuda.synchronize()
+    assert_lora_close(y, want, what=f"expand / {name}")
+    assert torch.equal(y.cpu()[none].view(torch.int16), p.y[none].view(torch.int16)), "rows without adapter changed"
+    k = len(p.b_slabs) - 1
+    y2 = d.y.clone()
+    lora_expand(tmp_in[k:].contiguous().to(DEV), d.b_slabs[k:], y2, *meta, offset_start=p.col_offsets[k], add_inputs=True)
+    torch.cuda.synchronize()
+    want2 = O.expand(p.y, tmp_in[k:].float(), p.b_slabs[k:], p.token_to_slot, p.col_offsets[k], True)
+    assert_lora_close(y2, want2, what=f"expand at an offset / {name}")
+    assert N.device_status(reset=True) == 0
+
+
 # ------------------------------------------------------ backend protocol / layers
 def test_backend_add_lora_contract():
     """tests/unit/test_lora_cuda.py:804-833 (fp16, scaling 0.5 -> [4, 10]) and the

@@ -194,8 +194,9 @@ def _worker(rank: int, world: int, port: int, results):
         x = torch.randn(T, hidden, generator=gen).to(torch.bfloat16)
         w = (torch.randn(out_f, hidden, generator=gen) * 0.05).to(torch.bfloat16)
         slots = torch.randint(-1, S, (T,), generator=gen, dtype=torch.int32)
-        adapters = {s: ((torch.randn(r, hidden, generator=gen) * 0.1).to(torch.bfloat16),
-                        (torch.randn(out_f, r, generator=gen) * 0.1).to(torch.bfloat16), 1.0 + 0.5 * s) for s in range(S)}
+        # (magnitudes chosen so that the delta stays of order one and the path's absolute bound applies to it)
+        adapters = {s: ((torch.randn(r, hidden, generator=gen) * 0.05).to(torch.bfloat16),
+                        (torch.randn(out_f, r, generator=gen) * 0.05).to(torch.bfloat16), 1.0 + 0.5 * s) for s in range(S)}
         a_full, b_full = torch.zeros(S, r, hidden), torch.zeros(S, out_f, r)
         for s, (a, b, sc) in adapters.items():
             O.write_slot(a_full, b_full, s, a.float(), b.float(), r, sc)
