@@ -86,7 +86,7 @@ def parse_args():
 
 
 def apply_options(args):
-    """--option key=value -> lora_b200_set_option (tuning runs and the ncu commands in profiles/)."""
+    """--option key=value -> lora_b200_set_option (tuning runs and profiler captures)."""
     from nanovllm_voxcpm_b200 import _native as N
 
     keys = {"cluster": N.OPT_CLUSTER, "pdl": N.OPT_PDL, "ring_kb": N.OPT_RING_KB,
@@ -129,13 +129,20 @@ def cpu_layer_inputs(seed=0):
     return projs
 
 
-def time_cpu_oracle(steps, warmup, budget_s=None):
-    """Reference formula on the host cores; one step = one layer (4 projections)."""
+def time_cpu_oracle(steps, warmup, budget_s=None, config="decode"):
+    """Reference formula on the host cores. One step = one layer (4 projections) of the decode configuration, the
+    single T = 64 linear of the CPU reference configuration (`config="reference_op"`), or one layer of the prefill
+    configuration (`config="prefill"`)."""
     from nanovllm_voxcpm_b200 import workloads as W
     from oracle import lora_oracle as O
 
     torch.set_num_threads(os.cpu_count() or 1)
-    projs = cpu_layer_inputs()
+    if config == "reference_op":
+        projs = [W.config1(seed=0)]
+    elif config == "prefill":
+        projs = [W.prefill_projection(name, seed=0) for name in W.PREFILL_LAYER]
+    else:
+        projs = cpu_layer_inputs()
     # fp32 copies so the timed part is the formula, not dtype conversion
     prepared = [(p.y.float(), p.x.float(), [a.float() for a in p.a_slabs], [b.float() for b in p.b_slabs],
                  p.token_to_slot, p.col_offsets) for p in projs]
@@ -520,7 +527,17 @@ def run_gpu_arm(args):
                 "value": r["gbs"], "unit": "GB/s", "cores": r["cores"], "kind": "port",
                 "sample": f"one layer (4 projections, {r['bytes'] / 1e6:.1f} MB algorithmic) x {r['iters']} iterations, "
                           f"fp32 torch CPU per-slot formula, median {r['ms']:.2f} ms",
+                # one CPU step is ONE layer; a step of the GPU arm is 24 layers: compare the GB/s, not the step times
+                "unit_of_work": "one layer per CPU step (the GPU step above is 24 layers)",
             }
+            if not args.no_extras:
+                # the same formula on the other two CPU-runnable configurations (bounded samples)
+                others = {}
+                for key, cfg_name, budget in (("reference_op_T64", "reference_op", 3.0), ("prefill_layer", "prefill", 12.0)):
+                    q = time_cpu_oracle(steps=20, warmup=2, budget_s=budget, config=cfg_name)
+                    others[key] = {"value": q["gbs"], "unit": "GB/s", "ms_per_step": q["ms"], "iterations": q["iters"],
+                                   "algorithmic_mb": q["bytes"] / 1e6}
+                line["cpu_baseline"]["other_configs"] = others
         line.update(extras)
         print(json.dumps(line))
     if world > 1:

@@ -343,6 +343,13 @@ int lora_b200_set_option(int32_t key, int32_t value);
  * for tests and health checks, not for the hot path. No counterpart in the reference. */
 int lora_b200_device_status(int32_t* status, int32_t reset);
 
+#ifdef B200_TRACE
+/* Tuning build only (the library compiled with -DB200_TRACE): copies `n_values` (<= 1024 * 32) SM-clock timestamps
+ * of the last fused-decode launch - 32 phase marks for each of the first 1024 slot buckets, taken by the first CTA of
+ * the bucket's cluster - into `out`. No counterpart in the reference. */
+int lora_b200_debug_trace(long long* out, int32_t n_values);
+#endif
+
 #ifdef __cplusplus
 }
 #endif

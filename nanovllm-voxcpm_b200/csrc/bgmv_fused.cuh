@@ -50,10 +50,6 @@ constexpr int kBgmvSmemMax = 232448;   // 227 KB opt-in maximum per CTA
 constexpr int kBgmvMaxStages = 12;
 constexpr int kBgmvMaxExpandTiles = 256;  // expand tiles of one CTA (entries of its tile table)
 
-// status bits of the device status word
-constexpr int kStatusWaitGaveUp = 1;
-
-__device__ int g_b200_status = 0;
 
 // Optional phase timeline (SM clock) of rank-0 CTAs, compiled in only for tuning builds.
 #ifdef B200_TRACE
@@ -101,6 +97,7 @@ struct BgmvParams {
   int tmp_bytes;    // bytes of one tmp buffer
   int off_red, off_tmp, off_tab, off_bar;
   int full_k;       // every K part has all 1024 columns
+  int y_cols;       // columns of y that the slices may touch (largest column end)
   int ksplit;       // 1: the K parts (not the rank rows) are dealt over the CTAs of a cluster
   int pitchR, recv_bytes, off_recv;  // K split: floats per token row / bytes of one buffer of received partial sums
   int use_pdl;
@@ -183,6 +180,8 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
   int rank = p.r_max;
   if (p.rank_per_slot != nullptr && slot >= 0 && slot < p.S) rank = min(max(p.rank_per_slot[slot], 0), p.r_max);
   const int r_eff = min(p.r_max, (rank + 31) & ~31);
+  // (a bucket whose row range leaves the batch is ignored; the bounds-checked build reports it)
+  if (cnt > 0 && slot >= 0) (void)B200_IN_BOUNDS(slot < p.S && start >= 0 && start <= p.T - cnt);
   if (slot < 0 || slot >= p.S || cnt <= 0 || start < 0 || start > p.T - cnt || r_eff == 0) {
     // An idle cluster holds nothing, but one CTA of every launch must outlive the previous launch
     // of the stream: a launch that ended before its predecessor would let the launch behind it
@@ -262,6 +261,11 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
           if (s == i_qs) aptr = p.st.a[s];
         const __nv_bfloat16* src =
             static_cast<const __nv_bfloat16*>(aptr) + ((int64_t)slot * p.r_max + i_qr) * in_dim + k0;
+        // 8 rank rows of slice i_qs, columns [k0, k0 + row_bytes / 2), into stage p_stage
+        if (!B200_IN_BOUNDS(aptr != nullptr && i_qs < n && i_qr + 8 <= p.r_max && k0 < in_dim && p_stage < NS &&
+                            8 * pitchA <= p.stage_bytes)) {
+          if (lane == 0) mbar_arrive(fb);  // the tile is skipped; its consumers see stale bytes, never a stuck barrier
+        } else
         if (nkp == 1) {
           // the 8 rows are contiguous in the slab: one copy (each copy costs the TMA unit ~100 cycles)
           if (lane == 0) {
@@ -295,6 +299,10 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
         }
         const int r0 = i_et << p.er_shift;
         const int nrows = min(ER, en - r0);
+        if (!B200_IN_BOUNDS(bptr != nullptr && nrows > 0 && lo + r0 + nrows <= out && p_stage < NS &&
+                            nrows * p.r_max * 2 <= p.stage_bytes)) {
+          if (lane == 0) mbar_arrive(fb);
+        } else
         if (lane == 0) {
           const uint32_t bytes = (uint32_t)nrows * (uint32_t)p.r_max * 2u;
           mbar_arrive_expect_tx(fb, bytes);
@@ -365,6 +373,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
   int tok0_lo = -1, tok0_hi = -1;
   if (g < cnt) tok0_lo = p.sorted_idx[start + g];
   if (g + 8 < cnt) tok0_hi = p.sorted_idx[start + g + 8];
+  (void)B200_IN_BOUNDS(tok0_lo < p.T && tok0_hi < p.T && tok0_lo >= -1 && tok0_hi >= -1);
   if (tok0_lo >= p.T) tok0_lo = -1;
   if (tok0_hi >= p.T) tok0_hi = -1;
 
@@ -448,6 +457,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
       tok_lo = tok_hi = -1;
       if (pass * kBgmvTok + g < cnt) tok_lo = p.sorted_idx[start + pass * kBgmvTok + g];
       if (pass * kBgmvTok + g + 8 < cnt) tok_hi = p.sorted_idx[start + pass * kBgmvTok + g + 8];
+      (void)B200_IN_BOUNDS(tok_lo < p.T && tok_hi < p.T && tok_lo >= -1 && tok_hi >= -1);
       if (tok_lo >= p.T) tok_lo = -1;
       if (tok_hi >= p.T) tok_hi = -1;
     }
@@ -648,7 +658,7 @@ __global__ void __launch_bounds__(kBgmvThreads, BGMV_MINBLOCKS) bgmv_fused_kerne
 #pragma unroll
         for (int j = 0; j < 4; ++j) mma_bf16_16816(d[j], alo.z, ahi.z, alo.w, ahi.w, w[j].z, w[j].w);
       }
-      if (y_col < (te.y & 0xffff)) {
+      if (y_col < (te.y & 0xffff) && B200_IN_BOUNDS(te.x >= 0 && te.x + y_col + 8 <= p.y_cols)) {
         const uint4 lo4 = make_uint4(pack_bf16x2(d[0][0], d[0][1]), pack_bf16x2(d[1][0], d[1][1]),
                                      pack_bf16x2(d[2][0], d[2][1]), pack_bf16x2(d[3][0], d[3][1]));
         const uint4 hi4 = make_uint4(pack_bf16x2(d[0][2], d[0][3]), pack_bf16x2(d[1][2], d[1][3]),
@@ -792,6 +802,8 @@ inline bool bgmv_plan(const BgmvProblem& b, BgmvParams* pp, const char** why) {
   p.off_tab = p.off_recv + 2 * p.recv_bytes;
   p.off_bar = p.off_tab + tab_bytes;
   p.full_k = (p.KP == kBgmvKP && b.in_dim % kBgmvKP == 0) ? 1 : 0;
+  p.y_cols = 0;
+  for (int s = 0; s < st.n; ++s) p.y_cols = std::max(p.y_cols, st.col[s] + st.out[s]);
   p.use_pdl = bgmv_options().pdl ? 1 : 0;
   p.mode = b.mode;
   p.tmp_io = b.tmp_io;

@@ -47,6 +47,28 @@ struct SliceTable {
 };
 
 // --------------------------------------------------------------- device side
+// Status word of the device (lora_b200_device_status): kernels never trap, they raise a bit and carry on.
+constexpr int kStatusWaitGaveUp = 1;        // a bounded wait on an mbarrier ran out
+constexpr int kStatusPeerWaitGaveUp = 2;    // a bounded wait on another rank's flag ran out
+constexpr int kStatusBadSmemBase = 4;       // dynamic shared memory was not 1024-byte aligned
+constexpr int kStatusBoundsViolation = 8;   // bounds-checked build only: an index left its array
+
+__device__ int g_b200_status = 0;
+
+// Bounds-checked build (-DB200_LORA_DEBUG_BOUNDS, lib/libb200lora_debug.so): every slot, row and column
+// index that comes from caller-provided metadata, and every copy range derived from it, is checked before
+// use; a violation raises kStatusBoundsViolation and the access is skipped. In the product build the checks
+// compile to nothing. (The pool's memory checker is not available to this project; this build takes its place.)
+#ifdef B200_LORA_DEBUG_BOUNDS
+__device__ __noinline__ bool bounds_violation() {
+  atomicOr(&g_b200_status, kStatusBoundsViolation);
+  return false;
+}
+#define B200_IN_BOUNDS(cond) ((cond) ? true : b200lora::bounds_violation())
+#else
+#define B200_IN_BOUNDS(cond) true
+#endif
+
 template <typename T>
 __device__ __forceinline__ float to_float(T v);
 template <>

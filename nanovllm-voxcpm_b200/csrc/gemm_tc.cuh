@@ -25,7 +25,6 @@
 namespace b200lora {
 
 constexpr int kTileThreads = 224;  // warp 0 TMA, warp 1 MMA + TMEM owner, warps 2-5 epilogue, warp 6 row mask
-constexpr int kStatusBadSmemBase = 4;  // device status bit: dynamic shared memory was not 1024-byte aligned
 constexpr int kTileSMs = 148;      // SMs of a B200: one persistent CTA each
 constexpr int kTileMaxSeg = 3;     // row blocks one CTA's tile range may touch
 #ifndef B200_GEMM_STAGES

@@ -22,6 +22,7 @@ generic_add_kernel(T* __restrict__ y, int64_t y_ld, const T* __restrict__ x, int
   extern __shared__ float tmp[];  // [n, r_max]
   const int t = blockIdx.x;
   const int slot = token_to_slot[t];
+  (void)B200_IN_BOUNDS(slot >= -1 && slot < S);
   if (slot < 0 || slot >= S) return;  // rows without an adapter are never touched
   int r = r_max;
   if (rank_per_slot != nullptr) r = min(max(rank_per_slot[slot], 0), r_max);

@@ -58,7 +58,8 @@ __device__ __forceinline__ void sgmv_find_runs(const int32_t* tts, int T, int S,
     const int row = row0 + i;
     int sl = -1;
     if (row < T) sl = tts[row];
-    if (sl >= S) sl = -1;
+    (void)B200_IN_BOUNDS(sl >= -1 && sl < S);  // ids outside [-1, S) are treated as "no adapter"; the checked build reports them
+    if (sl >= S || sl < -1) sl = -1;
     s_slot[i] = (TS)sl;
   }
   __syncthreads();

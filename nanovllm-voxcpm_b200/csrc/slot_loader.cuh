@@ -41,6 +41,13 @@ __device__ __forceinline__ float slot_load_src(const uint8_t* base, int dtype, i
 __global__ void __launch_bounds__(kSlotLoadThreads) slot_load_kernel(const SlotLoadDesc* __restrict__ table,
                                                                      const uint8_t* __restrict__ staging) {
   const SlotLoadDesc d = table[blockIdx.y];
+  // descriptor sanity (bounds-checked build): kinds, dtypes, and the data corner inside both the slot region
+  // and the payload's row pitch
+  if (!B200_IN_BOUNDS(d.dst != nullptr && d.kind >= 0 && d.kind <= 2 && d.dst_dtype >= 0 && d.dst_dtype <= 2 &&
+                      (d.kind != 0 || (d.src_dtype >= 0 && d.src_dtype <= 2 && d.dst_rows >= 0 && d.dst_cols >= 0 &&
+                                       d.src_rows >= 0 && d.src_rows <= d.dst_rows && d.src_cols >= 0 &&
+                                       d.src_cols <= d.dst_cols && d.src_cols <= d.src_ld && d.src_offset >= 0))))
+    return;
   if (d.kind == 1) {
     if (blockIdx.x == 0 && threadIdx.x == 0) *static_cast<int32_t*>(d.dst) = d.ivalue;
     return;

@@ -29,7 +29,6 @@ namespace b200lora {
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpMaxCtas = 64;
 constexpr int kTpThreads = 256;
-constexpr int kStatusPeerWaitGaveUp = 2;
 constexpr int kTpSpinLimit = 1 << 21;  // default poll limit of a system-scope load: about a second
 
 // polls after which the wait for a peer's flag gives up (lora_b200_set_option, B200_LORA_OPT_PEER_POLL_LIMIT)

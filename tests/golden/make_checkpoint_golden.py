@@ -20,7 +20,10 @@ import types
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("LORA_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("LORA_REFERENCE_ROOT") or (sys.argv[1] if len(sys.argv) > 1 else None)
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("usage: LORA_REFERENCE_ROOT=<checkout of the reference project> python " + os.path.basename(__file__)
+                     + "   (or pass the path as the first argument)")
 sys.path.insert(0, REF)
 sys.path.insert(0, HERE)
 
