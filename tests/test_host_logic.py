@@ -191,3 +191,42 @@ def test_metadata_slicing():
                              torch.tensor([0, 6], dtype=torch.int32), False, 1)
     tts, srt, cnt, off, ids, flag, n = meta.as_kernel_metadata(4)
     assert tts.numel() == 4 and srt.numel() == 4 and cnt.tolist() == [6] and n == 1 and flag is False
+
+
+def test_mixed_step_context_has_one_eager_plan_per_row_range():
+    """A step of decode rows followed by prefill chunks: every range carries the metadata that the eager builder
+    gives for its own rows, empty ranges are skipped, and the whole context is 'no adapter' only if every range is."""
+    slots = torch.tensor([2, -1, 0, 2, 5, 5, 5, 5, -1, -1, 1, 1], dtype=torch.int32)
+    ctx = CTX.build_mixed_lora_context(slots, [4, 4, 8])  # [0,4) decode, [4,4) empty, [4,8) chunk, [8,12) chunk
+    assert [(lo, hi) for lo, hi, _ in ctx.parts] == [(0, 4), (4, 8), (8, 12)]
+    assert not ctx.no_lora_flag and ctx.num_active_loras == 2
+    assert torch.equal(ctx.token_to_slot, slots)
+    for lo, hi, part in ctx.parts:
+        want = CTX.build_lora_context_from_token_to_slot(slots[lo:hi])
+        for name in ("token_to_slot", "token_indices_sorted_by_slot", "active_slot_ids", "num_tokens_per_slot",
+                     "slot_start_offsets"):
+            a, b = getattr(part, name), getattr(want, name)
+            assert (a is None and b is None) or torch.equal(a, b), name
+        assert part.no_lora_flag == want.no_lora_flag and part.num_active_loras == want.num_active_loras
+        # row indices are relative to the range
+        if part.token_indices_sorted_by_slot is not None:
+            assert int(part.token_indices_sorted_by_slot.max()) < hi - lo
+    none = CTX.build_mixed_lora_context(torch.full((6,), -1, dtype=torch.int32), [2])
+    assert none.no_lora_flag and all(p[2].no_lora_flag for p in none.parts)
+
+
+@pytest.mark.parametrize("case", [c for c in cases.LAYER_CASES if c.get("tp", 1) == 1], ids=lambda c: c["name"])
+def test_layers_split_a_mixed_step_per_row_range(case):
+    """With a mixed-step context the layers issue one multi-LoRA call per row range; the result equals the
+    single-call result on the same rows (the op is row-wise)."""
+    inputs = cases.build_inputs(case)
+    layer, x = build_b200_layer(L, case, inputs, 0)
+    T = x.shape[0]
+    CTX.set_lora_context(CTX.build_lora_context_from_token_to_slot(inputs["slots"]))
+    with torch.no_grad():
+        whole = layer(x)
+    CTX.set_lora_context(CTX.build_mixed_lora_context(inputs["slots"], [T // 3, T // 3, (2 * T) // 3]))
+    with torch.no_grad():
+        split = layer(x)
+    CTX.reset_lora_context()
+    torch.testing.assert_close(split, whole, atol=1e-6, rtol=1e-6)
