@@ -72,6 +72,8 @@ def parse_args():
                     help="--workload backbone5 under torchrun: one tensor-parallel group, or one replica per GPU")
     ap.add_argument("--slab-gb", type=float, default=80.0, help="--workload backbone5: HBM budget of the adapter slabs per GPU")
     ap.add_argument("--no-base", action="store_true", help="--workload backbone5: skip the run without adapters")
+    ap.add_argument("--extras-limit", type=float, default=420.0,
+                    help="seconds after which the additional blocks of the line are cut short and the line is printed without them")
     ap.add_argument("--no-extras", action="store_true",
                     help="decode workload: only the headline measurement (no secondary / reference_gpu / backbone / tp blocks)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "linear", "backbone", "backbone5", "tp", "admission", "glue"],
@@ -463,40 +465,9 @@ def run_gpu_arm(args):
                "per_rank_host_link_gbs": (h2d + d2h) / (e2e_ms / n_e2e * 1e-3) / 1e9,
                "per_rank_value": bytes_per_step / (e2e_ms / n_e2e * 1e-3) / 1e9, "cpu_binding": binding}
 
-    # ---- further blocks of the same line (skipped by --no-extras and in tuning runs of a subset) --------------
-    extras = {}
-    if not args.no_extras and args.only is None and args.layers == N_LAYERS and graph is not None:
-        import copy
-
-        def guarded(fn):
-            try:
-                return fn()
-            except Exception as exc:  # a block that cannot run is reported, the headline stays
-                return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
-
-        def brief(line, keys):
-            return {k: line[k] for k in keys if k in line} if "unavailable" not in line else line
-
-        if world == 1:
-            # the tensor-core kernels: prefill add (HBM-bound) and fused base GEMM + LoRA (tensor-bound)
-            sec = {}
-            for wl in ("prefill", "linear"):
-                a2 = copy.copy(args)
-                a2.workload, a2.only, a2.steps, a2.warmup = wl, None, 10, 3
-                sec[wl] = guarded(lambda a2=a2: brief(run_prefill_arm(a2, emit=False),
-                                                      ("metric", "value", "unit", "ms_per_step", "roofline", "us_per_projection",
-                                                       "clocks", "cublas_plus_prefill_add_ms_per_step", "lora_tflops")))
-            extras["secondary"] = sec
-            # the incumbent on the same GPU and inputs: the unmodified reference package's own Triton backend
-            a3 = copy.copy(args)
-            a3.workload, a3.only, a3.steps, a3.warmup = "decode", None, 10, 3
-            extras["reference_gpu"] = guarded(lambda: brief(run_reference_gpu_arm(a3, emit=False),
-                                                            ("value", "unit", "ms_per_step", "us_per_projection_call", "launch_mode",
-                                                             "backend", "unavailable")))
-        extras["backbone"] = guarded(lambda: backbone_replicas_block(device, world))
-        if world > 1:
-            extras["tp"] = guarded(lambda: tp_block(device, world, rank))
+    # ---- the headline line is complete here; what follows can only add blocks to it ----------------------------
     status_word = N.device_status()
+    line = None
     if rank == 0:
         peak, peak_kind = measured_peak()
         per_launch_s = ms_per_step * 1e-3 / launches_per_step
@@ -521,27 +492,127 @@ def run_gpu_arm(args):
         }
         if e2e is not None:
             line["e2e"] = e2e
-        if world == 1 and not args.no_cpu_baseline:
-            r = time_cpu_oracle(steps=40, warmup=3, budget_s=15.0)
-            line["cpu_baseline"] = {
-                "value": r["gbs"], "unit": "GB/s", "cores": r["cores"], "kind": "port",
-                "sample": f"one layer (4 projections, {r['bytes'] / 1e6:.1f} MB algorithmic) x {r['iters']} iterations, "
-                          f"fp32 torch CPU per-slot formula, median {r['ms']:.2f} ms",
-                # one CPU step is ONE layer; a step of the GPU arm is 24 layers: compare the GB/s, not the step times
-                "unit_of_work": "one layer per CPU step (the GPU step above is 24 layers)",
-            }
-            if not args.no_extras:
-                # the same formula on the other two CPU-runnable configurations (bounded samples)
-                others = {}
-                for key, cfg_name, budget in (("reference_op_T64", "reference_op", 3.0), ("prefill_layer", "prefill", 12.0)):
-                    q = time_cpu_oracle(steps=20, warmup=2, budget_s=budget, config=cfg_name)
-                    others[key] = {"value": q["gbs"], "unit": "GB/s", "ms_per_step": q["ms"], "iterations": q["iters"],
-                                   "algorithmic_mb": q["bytes"] / 1e6}
-                line["cpu_baseline"]["other_configs"] = others
-        line.update(extras)
-        print(json.dumps(line))
+
+    # ---- further blocks of the same line (skipped by --no-extras and in tuning runs of a subset) --------------
+    extras = {}
+    emit = _LineEmitter(line, extras, rank)
+    if not args.no_extras and args.only is None and args.layers == N_LAYERS and graph is not None:
+        import copy
+
+        # A block that stalls (a rank that left a collective early, a box in trouble) must not cost the headline:
+        # after the limit rank 0 prints the line with the blocks it has and every rank leaves.
+        emit.arm(args.extras_limit)
+
+        def guarded(fn):
+            try:
+                return fn()
+            except Exception as exc:  # a block that cannot run is reported, the headline stays
+                return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+
+        def brief(line, keys):
+            return {k: line[k] for k in keys if k in line} if "unavailable" not in line else line
+
+        if world == 1:
+            # the tensor-core kernels: prefill add (HBM-bound) and fused base GEMM + LoRA (tensor-bound)
+            sec = {}
+            extras["secondary"] = sec
+            for wl in ("prefill", "linear"):
+                a2 = copy.copy(args)
+                a2.workload, a2.only, a2.steps, a2.warmup = wl, None, 10, 3
+                sec[wl] = guarded(lambda a2=a2: brief(run_prefill_arm(a2, emit=False),
+                                                      ("metric", "value", "unit", "ms_per_step", "roofline", "us_per_projection",
+                                                       "clocks", "cublas_plus_prefill_add_ms_per_step", "lora_tflops")))
+            # the incumbent on the same GPU and inputs: the unmodified reference package's own Triton backend
+            a3 = copy.copy(args)
+            a3.workload, a3.only, a3.steps, a3.warmup = "decode", None, 10, 3
+            extras["reference_gpu"] = guarded(lambda: brief(run_reference_gpu_arm(a3, emit=False),
+                                                            ("value", "unit", "ms_per_step", "us_per_projection_call", "launch_mode",
+                                                             "backend", "unavailable")))
+        extras["backbone"] = guarded(lambda: backbone_replicas_block(device, world))
+        if world > 1:
+            extras["tp"] = guarded(lambda: tp_block(device, world, rank))
+        try:
+            line_status = N.device_status()
+            if rank == 0 and line_status != status_word:
+                line["device_status"] = line_status
+        except Exception:
+            pass
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        r = time_cpu_oracle(steps=40, warmup=3, budget_s=15.0)
+        line["cpu_baseline"] = {
+            "value": r["gbs"], "unit": "GB/s", "cores": r["cores"], "kind": "port",
+            "sample": f"one layer (4 projections, {r['bytes'] / 1e6:.1f} MB algorithmic) x {r['iters']} iterations, "
+                      f"fp32 torch CPU per-slot formula, median {r['ms']:.2f} ms",
+            # one CPU step is ONE layer; a step of the GPU arm is 24 layers: compare the GB/s, not the step times
+            "unit_of_work": "one layer per CPU step (the GPU step above is 24 layers)",
+        }
+        if not args.no_extras:
+            # the same formula on the other two CPU-runnable configurations (bounded samples)
+            others = {}
+            for key, cfg_name, budget in (("reference_op_T64", "reference_op", 3.0), ("prefill_layer", "prefill", 12.0)):
+                q = time_cpu_oracle(steps=20, warmup=2, budget_s=budget, config=cfg_name)
+                others[key] = {"value": q["gbs"], "unit": "GB/s", "ms_per_step": q["ms"], "iterations": q["iters"],
+                               "algorithmic_mb": q["bytes"] / 1e6}
+            line["cpu_baseline"]["other_configs"] = others
+    emit.disarm()
+    emit()
     if world > 1:
-        dist.destroy_process_group()
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+class _LineEmitter:
+    """Prints rank 0's JSON line exactly once: at the normal end, or - if the additional blocks do not finish
+    within their limit, or the launcher ends the job because another rank failed - from a watchdog thread /
+    the SIGTERM handler, with the blocks that are complete and a note; the process then leaves with status 0."""
+
+    def __init__(self, line, extras, rank):
+        import threading
+
+        self.line, self.extras, self.rank = line, extras, rank
+        self._lock = threading.Lock()
+        self._done = False
+        self._timer = None
+
+    def __call__(self, note=None):
+        with self._lock:
+            if self._done:
+                return
+            self._done = True
+            if self.rank == 0 and self.line is not None:
+                out = dict(self.line)
+                out.update(self.extras)
+                if note:
+                    out["extras_note"] = note
+                print(json.dumps(out, default=str), flush=True)
+
+    def _bail(self, note):
+        self(note)
+        sys.stdout.flush()
+        os._exit(0)
+
+    def arm(self, limit_s):
+        import signal
+        import threading
+
+        if limit_s and limit_s > 0:
+            # rank 0 speaks first; the other ranks leave a moment later
+            delay = limit_s + (0.0 if self.rank == 0 else 5.0)
+            self._timer = threading.Timer(delay, self._bail, args=(f"additional blocks cut short after {limit_s:.0f} s",))
+            self._timer.daemon = True
+            self._timer.start()
+        if self.rank == 0:
+            try:
+                signal.signal(signal.SIGTERM, lambda signum, frame: self._bail("additional blocks cut short: job terminated"))
+            except ValueError:  # not the main thread
+                pass
+
+    def disarm(self):
+        if self._timer is not None:
+            self._timer.cancel()
+            self._timer = None
 
 
 # ------------------------------------------------------------------ secondary workloads (prefill kernels)
