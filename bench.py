@@ -1446,19 +1446,22 @@ def tp_block(device, world, rank):
         return BB.time_mixed_step(m, n_dec, lens, dec, pre, context_len=40, iters=1, warmup=1)[2].float()
 
     out_tp = run_small("peer_exchange")
-    parity = "ok"
+    parity, parity_detail = "ok", None
     if rank == 0:
         _replica_layers(True)
         try:
             out_1 = run_small("partial_y")
         finally:
             _replica_layers(False)
-        err = float((out_tp - out_1).abs().max())
-        parity = "ok" if err <= 6e-2 and float(out_1.abs().max()) > 0.1 else f"max-abs difference {err:.3g}"
+        err, ref_max = float((out_tp - out_1).abs().max()), float(out_1.abs().max())
+        # two bf16 decoder layers summed in another order per rank count: 6e-2 absolute plus 1 % of the largest
+        # output (one bf16 step at that magnitude), the bound the tests use for bf16 stacks
+        parity = "ok" if err <= 6e-2 + 1e-2 * ref_max and ref_max > 0.1 else f"max-abs difference {err:.3g} (largest output {ref_max:.3g})"
+        parity_detail = {"max_abs_difference": err, "largest_output": ref_max}
     # ---- (2) the 8-GPU class layers under TP = N
     tokens, ms, info, model, exchange = measure_config5(device, 8, 40.0, 3)
     ms = _max_over_ranks(ms, device, world)
-    block = {"parallelism": f"tp{world}", "tp_parity": parity,
+    block = {"parallelism": f"tp{world}", "tp_parity": parity, "tp_parity_detail": parity_detail,
              "workload": "8 layers of the 8-GPU class decoder (hidden 4096, 32/8 heads x 128, intermediate 14336), "
                          f"{N_DECODE_5} decode rows + {sum(PREFILL_LENS_5)}-token prefill chunk per step",
              "tokens_per_s": tokens / (ms * 1e-3), "ms_per_step": ms, **info,
