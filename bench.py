@@ -1348,6 +1348,7 @@ def run_backbone5_arm(args):
 
     world, rank, local = _ranks()
     torch.cuda.set_device(local)
+    apply_options(args)
     device = torch.device("cuda", local)
     if world > 1:
         _init_dist(device)

@@ -215,6 +215,15 @@ def test_shrink_and_expand_ops_match_oracle():
     lora_shrink(x.to(DEV), [a.to(DEV)], out, *meta, 0.5)
     assert_lora_close(out, O.shrink(x, [a], slots, 0.5), max_abs=5e-2, rel=5e-2)
 
+    # the reference's split-K shape (tests/unit/test_lora_cuda.py:875-911): K = 4096, rank 1, same metadata; its own
+    # bound is 2e-1 (bf16 atomics over the K splits), here the sum is kept in fp32 and rounded once
+    x = torch.randn(4, 4096, generator=g).to(dtype)
+    a = torch.randn(2, 1, 4096, generator=g).to(dtype)
+    out = torch.empty((1, 4, 1), device=DEV, dtype=dtype)
+    lora_shrink(x.to(DEV), [a.to(DEV)], out, *meta, 0.5)
+    want = O.shrink(x, [a], slots, 0.5)
+    torch.testing.assert_close(out.float().cpu(), want, atol=5e-2, rtol=1e-2)
+
     # bf16, two slices, fp32 intermediate (the row-parallel [T, r] exchange format)
     p = W.make_projection(31, 50, 256, [64, 32], 4, 16, p_none=0.2)
     d = p.to_device(DEV)
