@@ -748,6 +748,13 @@ inline bool bgmv_plan(const BgmvProblem& b, BgmvParams* pp, const char** why) {
     const double nb = (double)b.n_buckets;
     const double in_use = nb * (1.0 - std::exp(-(double)std::max(b.T, 1) / nb));
     C = in_use <= 56.0 ? 4 : (in_use <= 112.0 ? 2 : 1);
+    // Large adapters (rank 64 on 4096-wide layers: 1 - 5 MB per bucket) keep an SM busy for tens of microseconds;
+    // then the balance over the SMs matters more than room for the next launch: at most 512 KB of slab per CTA.
+    // Measured on a 4-layer slice of a 32-head decoder, 512 rows over 175 adapters: 20.8 ms per step with one CTA
+    // per bucket, 19.7 with 2, 19.0 with 4.
+    int64_t bucket_bytes = 0;
+    for (int s = 0; s < st.n; ++s) bucket_bytes += 2 * (int64_t)b.r_max * ((int64_t)b.in_dim + st.out[s]);
+    while (C < 4 && bucket_bytes / C > 512 * 1024) C *= 2;
   }
   // K split: at least one K part (1024 columns) per CTA of the cluster and all rank rows in one CTA;
   // the shrink-only / expand-only pair of the tensor-parallel exchange keeps the row split
